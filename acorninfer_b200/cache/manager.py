@@ -3,7 +3,8 @@ state of fixed size in slots, and the bookkeeping of who holds what.
 
 Layers are sorted into *groups* by what they need (``KVNeeds.group_key``: head count,
 head size, all keys or a window of them).  A group has a page pool of its own and one
-storage tensor ``[layers_in_group, 2, num_pages, kv_heads, page_size, head_dim]``: a page
+storage tensor ``[layers_in_group, 2, num_pages, kv_heads, page_size, head_dim]`` (1 instead of 2 for
+groups that keep no separate values): a page
 id names the same page in every layer of its group.  A request has one block table per
 group; the token at position p lives in ``table[p // page_size - page_base]``, slot
 ``p % page_size``.  ``page_base`` counts pages given back at the front of a windowed
@@ -102,7 +103,7 @@ class CacheManager:
             import torch
             for g in self.groups:
                 n = g.needs
-                g.storage = torch.zeros((len(g.entries), 2, g.pool.total + 1, n.num_kv_heads, page_size, n.head_dim),
+                g.storage = torch.zeros((len(g.entries), 2 if n.values else 1, g.pool.total + 1, n.num_kv_heads, page_size, n.head_dim),
                                         dtype=n.dtype or dtype, device=device)
             for entry, sn in self.state_needs.items():
                 self.state[entry] = torch.zeros((num_slots + 1, *sn.shape), dtype=sn.dtype or torch.float32,
@@ -111,10 +112,11 @@ class CacheManager:
     # ------------------------------------------------------------------ storage views
 
     def kv_pages(self, entry: int):
-        """(k_pages, v_pages) of a schedule entry: each [num_pages, nkv, P, d]."""
+        """(k_pages, v_pages) of a schedule entry: each [num_pages, nkv, P, d]; v_pages None for a
+        group that keeps one row per token only."""
         gi, li = self.entry_group[entry]
         st = self.groups[gi].storage
-        return st[li, 0], st[li, 1]
+        return st[li, 0], (st[li, 1] if st.shape[1] > 1 else None)
 
     def group_of(self, entry: int) -> int:
         return self.entry_group[entry][0]
@@ -123,7 +125,7 @@ class CacheManager:
         total = 0
         for g in self.groups:
             width = 2 if g.storage is None else g.storage.element_size()
-            total += len(g.entries) * 2 * g.needs.num_kv_heads * g.needs.head_dim * width
+            total += len(g.entries) * (2 if g.needs.values else 1) * g.needs.num_kv_heads * g.needs.head_dim * width
         return total
 
     # ------------------------------------------------------------------ requests

@@ -165,6 +165,237 @@ class Qwen3Config(ModelConfig):
         return out
 
 
+# --------------------------------------------------------------------------- Kogonex
+
+
+def _sub(raw: dict, key: str, where: str, required: bool = True):
+    """``raw[key]`` as a JSON object (None if absent and not required)."""
+    v = raw.get(key)
+    if v is None:
+        if required:
+            raise ConfigError(f"config.json: {where}'{key}' is missing")
+        return None
+    if not isinstance(v, dict):
+        raise ConfigError(f"config.json: {where}'{key}' must be an object, got {v!r}")
+    return v
+
+
+@dataclass(frozen=True)
+class RotaryScaling:
+    """Frequency scaling of rotary positions for contexts beyond the trained one: pairs that turn
+    more than ``fast`` times over ``original`` positions keep their frequency, pairs that turn less
+    than ``slow`` times are slowed by ``factor``, a linear ramp between."""
+
+    factor: float
+    original: int
+    fast: float
+    slow: float
+
+
+@dataclass(frozen=True)
+class LatentAttentionConfig:
+    """Attention whose keys and values are up-projections of one cached latent per token."""
+
+    kind: ClassVar[str] = "latent_attention"
+    heads: int
+    dim: int                     # unrotated query/key entries per head
+    rot_dim: int                 # rotated entries per head; the rotated key part is shared by all heads
+    vdim: int
+    kv_rank: int
+    scale: float
+    rot_dims: int                # entries of the rotated part that are really rotated
+    rot_base: float
+    scaling: RotaryScaling | None = None
+    window: int | None = None    # a query sees itself and the window - 1 tokens before it
+    kv_from: int | None = None   # layer whose cached latent and key part this layer reads
+
+    @classmethod
+    def from_dict(cls, m: dict, where: str) -> "LatentAttentionConfig":
+        rot = _sub(m, "rot", where)
+        sc = _sub(rot, "scaling", where + "rot.", required=False)
+        mask = _sub(m, "mask", where, required=False)
+        return cls(
+            heads=_take(m, "heads", int), dim=_take(m, "dim", int), rot_dim=_take(m, "rot_dim", int),
+            vdim=_take(m, "vdim", int), kv_rank=_take(m, "kv_rank", int), scale=_take(m, "scale", float),
+            rot_dims=_take(rot, "dims", int), rot_base=_take(rot, "base", float),
+            scaling=None if sc is None else RotaryScaling(_take(sc, "factor", float), _take(sc, "original", int),
+                                                          _take(sc, "fast", float), _take(sc, "slow", float)),
+            window=None if mask is None else _take(mask, "size", int),
+            kv_from=_take(m, "kv_from", int, None))
+
+    def to_dict(self) -> dict:
+        rot: dict = {"base": self.rot_base, "dims": self.rot_dims}
+        if self.scaling is not None:
+            rot["scaling"] = asdict(self.scaling)
+        out: dict = {"dim": self.dim, "heads": self.heads, "kv_rank": self.kv_rank, "rot": rot, "rot_dim": self.rot_dim,
+                     "scale": self.scale, "vdim": self.vdim}
+        if self.window is not None:
+            out["mask"] = {"size": self.window}
+        if self.kv_from is not None:
+            out["kv_from"] = self.kv_from
+        return out
+
+
+@dataclass(frozen=True)
+class ChannelDeltaConfig:
+    """Gated delta rule with a decay per key channel and short convolutions on q, k, v."""
+
+    kind: ClassVar[str] = "channel_delta"
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    conv: int
+    # Inner sizes of the decay's and the gate's low-rank projections.  A checkpoint's tensors fix them;
+    # they are needed (and written as "decay_rank" / "gate_rank") only to make a model from nothing.
+    decay_rank: int | None = None
+    gate_rank: int | None = None
+
+    @classmethod
+    def from_dict(cls, m: dict, where: str) -> "ChannelDeltaConfig":
+        return cls(heads=_take(m, "heads", int), kv_heads=_take(m, "kv_heads", int), dim=_take(m, "dim", int),
+                   vdim=_take(m, "vdim", int), conv=_take(m, "conv", int),
+                   decay_rank=_take(m, "decay_rank", int, None), gate_rank=_take(m, "gate_rank", int, None))
+
+    def to_dict(self) -> dict:
+        out = {"conv": self.conv, "dim": self.dim, "heads": self.heads, "kv_heads": self.kv_heads, "vdim": self.vdim}
+        if self.decay_rank is not None:
+            out["decay_rank"] = self.decay_rank
+        if self.gate_rank is not None:
+            out["gate_rank"] = self.gate_rank
+        return out
+
+
+@dataclass(frozen=True)
+class RoutedExpertsConfig:
+    """A routed mixture of small SwiGLU experts; the last ``identity`` router outputs return their input."""
+
+    ff: int
+    experts: int
+    identity: int
+    top: int
+    groups: int = 1
+    keep: int = 1
+
+    @classmethod
+    def from_dict(cls, f: dict, where: str) -> "RoutedExpertsConfig":
+        kind = f.get("kind", "moe")
+        if kind != "moe":
+            raise ConfigError(f"config.json: {where}'kind' must be 'moe', got {kind!r}")
+        r = _sub(f, "router", where)
+        g = _sub(r, "groups", where + "router.", required=False)
+        return cls(ff=_take(_sub(f, "expert", where), "ff", int), experts=_take(r, "experts", int),
+                   identity=_take(r, "identity", int, 0), top=_take(r, "top", int),
+                   groups=1 if g is None else _take(g, "count", int), keep=1 if g is None else _take(g, "keep", int))
+
+    def to_dict(self) -> dict:
+        return {"expert": {"ff": self.ff}, "kind": "moe",
+                "router": {"experts": self.experts, "groups": {"count": self.groups, "keep": self.keep},
+                           "identity": self.identity, "top": self.top}}
+
+
+_KOGONEX_MIXERS = {c.kind: c for c in (LatentAttentionConfig, ChannelDeltaConfig)}
+
+
+@dataclass(frozen=True)
+class KogonexLayer:
+    mixer: LatentAttentionConfig | ChannelDeltaConfig
+    mlp: RoutedExpertsConfig | None
+
+
+@dataclass(frozen=True)
+class KogonexConfig(ModelConfig):
+    """Kogonex: a token table plus hashed bigram rows; layers that add the RMS norm of each
+    sublayer's output to the stream (``x += norm(mixer(x))``, ``x += norm(ff(x))``), with a mixer that
+    is either attention through a cached latent (sliding window, sink, scaled rotary positions,
+    optionally reading an earlier layer's cache) or a gated delta rule, and routed experts as
+    feed-forward (or none); a final norm and an output matrix.  ``config.json`` lists the layers
+    in order, each with its own sizes."""
+
+    architecture: ClassVar[str] = "Kogonex"
+
+    vocab_size: int
+    hidden_size: int
+    norm_eps: float
+    layers: tuple[KogonexLayer, ...]
+    bigram_buckets: int | None = None
+    bigram_mul_prev: int = 0
+    bigram_mul_cur: int = 0
+    eos_token_id: tuple[int, ...] = field(default_factory=tuple)
+
+    def __post_init__(self) -> None:
+        if self.vocab_size < 1 or self.hidden_size < 1 or not self.layers:
+            raise ConfigError("config.json: 'vocab', 'width' must be >= 1 and 'layers' non-empty")
+        if not self.norm_eps > 0:
+            raise ConfigError(f"config.json: norm 'eps' must be > 0, got {self.norm_eps}")
+        if self.bigram_buckets is not None and self.bigram_buckets < 1:
+            raise ConfigError("config.json: bigram 'buckets' must be >= 1")
+        for i, layer in enumerate(self.layers):
+            m, w = layer.mixer, f"layers[{i}].mixer."
+            if isinstance(m, LatentAttentionConfig):
+                if min(m.heads, m.dim, m.vdim, m.kv_rank) < 1 or m.rot_dim < 0:
+                    raise ConfigError(f"config.json: {w}sizes must be >= 1")
+                if m.rot_dims % 2 or not (0 <= m.rot_dims <= m.rot_dim):
+                    raise ConfigError(f"config.json: {w}rot.dims must be even and at most rot_dim, got {m.rot_dims}")
+                if m.window is not None and m.window < 1:
+                    raise ConfigError(f"config.json: {w}mask.size must be >= 1, got {m.window}")
+                if m.kv_from is not None:
+                    src = self.layers[m.kv_from].mixer if 0 <= m.kv_from < i else None
+                    if not isinstance(src, LatentAttentionConfig) or src.kv_from is not None:
+                        raise ConfigError(f"config.json: {w}kv_from must name an earlier latent_attention layer "
+                                          "that keeps its own cache")
+                    if (src.kv_rank, src.rot_dim, src.rot_dims, src.rot_base, src.scaling) != \
+                            (m.kv_rank, m.rot_dim, m.rot_dims, m.rot_base, m.scaling):
+                        raise ConfigError(f"config.json: {w}kv_rank, rot_dim and rot must equal those of layer {m.kv_from}")
+            else:
+                if min(m.heads, m.kv_heads, m.dim, m.vdim, m.conv) < 1 or m.heads % m.kv_heads:
+                    raise ConfigError(f"config.json: {w}sizes must be >= 1 and 'heads' a multiple of 'kv_heads'")
+            f = layer.mlp
+            if f is not None:
+                n = f.experts + f.identity
+                if min(f.ff, f.top, f.groups, f.keep) < 1 or f.experts < 0 or f.identity < 0 or n < 1:
+                    raise ConfigError(f"config.json: layers[{i}].mlp sizes must be positive")
+                if n % f.groups or f.keep > f.groups or f.top > f.keep * (n // f.groups):
+                    raise ConfigError(f"config.json: layers[{i}].mlp: {n} router outputs do not split into {f.groups} groups "
+                                      f"of which {f.keep} hold {f.top} choices")
+
+    @classmethod
+    def from_dict(cls, raw: dict) -> "KogonexConfig":
+        layers_raw = raw.get("layers")
+        if not isinstance(layers_raw, list) or not layers_raw:
+            raise ConfigError("config.json: 'layers' must be a non-empty list")
+        layers = []
+        for i, lr in enumerate(layers_raw):
+            where = f"layers[{i}]."
+            kind = lr.get("type") if isinstance(lr, dict) else None
+            if kind not in _KOGONEX_MIXERS:
+                raise ConfigError(f"config.json: {where}'type' must be one of {sorted(_KOGONEX_MIXERS)}, got {kind!r}")
+            mixer = _KOGONEX_MIXERS[kind].from_dict(_sub(lr, "mixer", where), where + "mixer.")
+            mlp = _sub(lr, "mlp", where, required=False)
+            layers.append(KogonexLayer(mixer, None if mlp is None else RoutedExpertsConfig.from_dict(mlp, where + "mlp.")))
+        emb = _sub(raw, "embedding", "", required=False) or {}
+        big = _sub(emb, "bigram", "embedding.", required=False)
+        eos = raw.get("eos_token_id")
+        eos_ids = () if eos is None else tuple(int(e) for e in (eos if isinstance(eos, (list, tuple)) else [eos]))
+        return cls(vocab_size=_take(raw, "vocab", int), hidden_size=_take(raw, "width", int),
+                   norm_eps=_take(_sub(raw, "norm", ""), "eps", float), layers=tuple(layers),
+                   bigram_buckets=None if big is None else _take(big, "buckets", int),
+                   bigram_mul_prev=0 if big is None else _take(big, "mul_prev", int),
+                   bigram_mul_cur=0 if big is None else _take(big, "mul_cur", int), eos_token_id=eos_ids)
+
+    def to_dict(self) -> dict:
+        out: dict = {"architecture": self.architecture, "vocab": self.vocab_size, "width": self.hidden_size,
+                     "norm": {"eps": self.norm_eps}}
+        if self.bigram_buckets is not None:
+            out["embedding"] = {"bigram": {"buckets": self.bigram_buckets, "mul_cur": self.bigram_mul_cur,
+                                           "mul_prev": self.bigram_mul_prev}}
+        out["layers"] = [{"type": l.mixer.kind, "mixer": l.mixer.to_dict(), "mlp": None if l.mlp is None else l.mlp.to_dict()}
+                         for l in self.layers]
+        if self.eos_token_id:
+            out["eos_token_id"] = list(self.eos_token_id)
+        return out
+
+
 def read_config_json(model_dir: str | Path) -> dict:
     path = Path(model_dir) / "config.json"
     if not path.is_file():
@@ -179,6 +410,8 @@ def read_config_json(model_dir: str | Path) -> dict:
 
 
 def architecture_name(raw: dict) -> str:
+    if isinstance(raw.get("architecture"), str):         # designs that name themselves with one string
+        return raw["architecture"]
     archs = raw.get("architectures")
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
         raise ConfigError("config.json: 'architectures' must be a non-empty list of names")

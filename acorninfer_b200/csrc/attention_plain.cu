@@ -8,6 +8,10 @@
 // the pages of its row: key j lives in page block_table[r * stride + j / P - page_base[r]], slot
 // j % P, cache layout [num_pages, nkv, P, d].  Query head h uses kv head h / (nq / nkv).
 // Scores, softmax (online, per chunk of keys) and the weighted sum are float32.
+// Values may be narrower than keys (dv <= d: the first dv elements of a value row are summed, the
+// output is [tokens, nq, dv]), which also serves a cache whose value rows are the key rows' heads
+// (v_pages == k_pages).  `sink` (one float per query head, or null) adds exp(sink) to the softmax
+// denominator.
 //
 // A chunk is 512 keys.  Scores: one thread a key, the dot products of all the block's query heads
 // in one pass over the key row (the rows reach the threads through a hand-over in shared memory, so
@@ -27,7 +31,7 @@ __global__ void __launch_bounds__(PLAIN_THREADS) attention_plain_kernel(
     const T* __restrict__ q, int64_t q_stride, T* __restrict__ out, const T* __restrict__ k_pages,
     const T* __restrict__ v_pages, const int* __restrict__ block_table, const int* __restrict__ page_base,
     int table_stride, const int* __restrict__ token_row, const int* __restrict__ positions, int nq, int nkv, int d,
-    int P, float scale, int window, int parts) {
+    int P, float scale, int window, int parts, int dv, const float* __restrict__ sink) {
     extern __shared__ __align__(16) float smem[];
     float* qs = smem;                                   // [heads][d], scaled
     float* sc = smem + PLAIN_HEADS * d;                 // [heads][PLAIN_THREADS] probabilities of the chunk
@@ -174,14 +178,14 @@ __global__ void __launch_bounds__(PLAIN_THREADS) attention_plain_kernel(
 #pragma unroll
         for (int a = 0; a < NACC; ++a) {
             const int dim = dlane + a * PLAIN_LANES;
-            if (a * PLAIN_LANES >= d) break;
+            if (a * PLAIN_LANES >= dv) break;
             for (int j0 = kgroup; j0 < n; j0 += 8 * PLAIN_KGROUPS) {
                 float v[8];
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
                     const int jj = j0 + u * PLAIN_KGROUPS;
                     v[u] = 0.f;
-                    if (jj < n && dim < d)
+                    if (jj < n && dim < dv)
                         v[u] = to_float(v_pages[row_at[jj] + dim]);
                 }
 #pragma unroll
@@ -202,20 +206,22 @@ __global__ void __launch_bounds__(PLAIN_THREADS) attention_plain_kernel(
     // (heads x 512 floats >= heads x 3 x 128 x dims handled one `a` at a time)
 #pragma unroll
     for (int a = 0; a < NACC; ++a) {
-        if (a * PLAIN_LANES >= d) break;
+        if (a * PLAIN_LANES >= dv) break;
 #pragma unroll
         for (int g = 0; g < PLAIN_HEADS; ++g)
             if (g < G && kgroup > 0) sc[g * PLAIN_THREADS + (kgroup - 1) * PLAIN_LANES + dlane] = acc[g][a];
         __syncthreads();
         const int dim = dlane + a * PLAIN_LANES;
-        if (kgroup == 0 && dim < d) {
+        if (kgroup == 0 && dim < dv) {
 #pragma unroll
             for (int g = 0; g < PLAIN_HEADS; ++g) {
                 if (g < G) {
                     float v = acc[g][a];
 #pragma unroll
                     for (int kg = 1; kg < PLAIN_KGROUPS; ++kg) v += sc[g * PLAIN_THREADS + (kg - 1) * PLAIN_LANES + dlane];
-                    out[((int64_t)t * nq + h0 + g) * d + dim] = from_float<T>(v / l[g]);
+                    // a sink is one more term of the denominator: it has no key (no scale) and no value
+                    const float denom = sink ? l[g] + expf(sink[h0 + g] - m[g]) : l[g];
+                    out[((int64_t)t * nq + h0 + g) * dv + dim] = from_float<T>(v / denom);
                 }
             }
         }
@@ -227,8 +233,9 @@ extern "C" int acorn_attention_plain(const void* q, int64_t q_stride, void* out,
                                      const void* v_pages, const int* block_table, const int* page_base,
                                      int table_stride, const int* token_row, const int* positions,
                                      int tokens, int nq, int nkv, int d, int P, float scale, int window,
-                                     int dtype, cudaStream_t stream) {
+                                     int dtype, int dv, const float* sink, cudaStream_t stream) {
     if (tokens <= 0) return 0;
+    if (dv < 1 || dv > d) return ACORN_ERR_UNSUPPORTED;
     if (d < 1 || d > PLAIN_MAX_D || nkv < 1 || nq % nkv != 0) return ACORN_ERR_UNSUPPORTED;
     const int parts = (nq / nkv + PLAIN_HEADS - 1) / PLAIN_HEADS;
     if ((int64_t)nkv * parts > 65535) return ACORN_ERR_UNSUPPORTED;
@@ -245,6 +252,6 @@ extern "C" int acorn_attention_plain(const void* q, int64_t q_stride, void* out,
     dim3 grid(tokens, nkv * parts);
     ACORN_DISPATCH_DTYPE(dtype, T, (attention_plain_kernel<T><<<grid, PLAIN_THREADS, smem, stream>>>(
         (const T*)q, q_stride, (T*)out, (const T*)k_pages, (const T*)v_pages, block_table, page_base,
-        table_stride, token_row, positions, nq, nkv, d, P, scale, window, parts)));
+        table_stride, token_row, positions, nq, nkv, d, P, scale, window, parts, dv, sink)));
     return acorn_launch_status();
 }

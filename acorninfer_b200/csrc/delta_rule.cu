@@ -1,0 +1,272 @@
+// Gated delta rule with one decay per key channel, as a recurrent mixer's kernels.
+//
+// Per head a state matrix S [dim, vdim] in float32, zero when a request starts, kept in the
+// request's state slot between steps.  For every token, with unit-length q and k (q times dim^-1/2),
+// a write strength beta and a decay g[d] per key channel, all float32:
+//     S[d, :] *= g[d];   u = beta * (v - S^T k);   S += k u^T;   o = S^T q.
+// The columns of S (one per value channel) never mix, so a block takes a head's columns in tiles.
+//
+//   delta_prep          per token: the short causal convolution over time of the q, k, v channels
+//                       (inputs before the step's first token come from the request's state), silu,
+//                       unit norms, beta = sigmoid(.), g = exp(-exp(A_log) softplus(. + dt_bias)),
+//                       the output gate sigmoid(.); float32 outputs
+//   conv_state_update   per row: the last taps - 1 convolution inputs into the request's state
+//   delta_rule          the recurrence over a row's tokens, state in registers
+//   delta_out           per token and head: o / rms(o) * w * gate
+//
+// The state slot is one float32 vector: S of all heads [H, dim, vdim], then the convolution inputs
+// [taps - 1, channels] in time order.
+#include "common.cuh"
+
+#define DELTA_MAX_TAPS 16
+
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float softplusf_(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+// main [T, C + H]: the q (KH*dim), k (KH*dim), v (H*vdim) channels before the convolution, then beta's
+// pre-activation per head.  up [T, H*dim + H*vdim] float32: the decay's and the gate's pre-activations.
+template <typename T>
+__global__ void delta_prep_kernel(const T* __restrict__ main_, int64_t ld, const float* __restrict__ up, int64_t ld_up,
+                                  const float* __restrict__ conv_w, const float* __restrict__ state, int64_t slot_stride,
+                                  int64_t conv_off, const float* __restrict__ A_log, const float* __restrict__ dt_bias,
+                                  const int* __restrict__ token_row, const int* __restrict__ row_start,
+                                  const int* __restrict__ row_slot, float* __restrict__ qn, float* __restrict__ kn,
+                                  float* __restrict__ vv, float* __restrict__ beta, float* __restrict__ g,
+                                  float* __restrict__ gate, int H, int KH, int dim, int vdim, int taps) {
+    extern __shared__ float act[];                      // [C] activations of the q, k, v channels
+    __shared__ float inv_norm[2 * 64];                  // per q head, per k head (KH <= 64)
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const int r = token_row[t];
+    const int i0 = t - row_start[r];                    // index of the token within its row
+    const int C = 2 * KH * dim + H * vdim;
+    const float* cstate = state + (int64_t)row_slot[r] * slot_stride + conv_off;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < taps; ++j) {
+            const int idx = i0 - (taps - 1) + j;        // input index within the row; negative: before the step
+            const float in = idx >= 0 ? to_float(main_[(int64_t)(t - i0 + idx) * ld + c])
+                                      : cstate[(int64_t)(taps - 1 + idx) * C + c];
+            acc = fmaf(conv_w[(int64_t)c * taps + j], in, acc);
+        }
+        act[c] = acc * sigmoidf_(acc);
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int hd = warp; hd < 2 * KH; hd += nwarps) {    // unit norms of the q heads, then of the k heads
+        float ss = 0.f;
+        for (int d = lane; d < dim; d += 32) ss += act[hd * dim + d] * act[hd * dim + d];
+        ss = warp_sum(ss);
+        if (lane == 0) inv_norm[hd] = rsqrtf(ss + 1e-6f);
+    }
+    __syncthreads();
+    const float qscale = rsqrtf((float)dim);
+    for (int c = threadIdx.x; c < KH * dim; c += blockDim.x) {
+        qn[(int64_t)t * KH * dim + c] = act[c] * inv_norm[c / dim] * qscale;
+        kn[(int64_t)t * KH * dim + c] = act[KH * dim + c] * inv_norm[KH + c / dim];
+    }
+    for (int c = threadIdx.x; c < H * vdim; c += blockDim.x) {
+        vv[(int64_t)t * H * vdim + c] = act[2 * KH * dim + c];
+        gate[(int64_t)t * H * vdim + c] = sigmoidf_(up[(int64_t)t * ld_up + H * dim + c]);
+    }
+    for (int c = threadIdx.x; c < H * dim; c += blockDim.x)
+        g[(int64_t)t * H * dim + c] = expf(-expf(A_log[c / dim]) * softplusf_(up[(int64_t)t * ld_up + c] + dt_bias[c]));
+    for (int h = threadIdx.x; h < H; h += blockDim.x) beta[(int64_t)t * H + h] = sigmoidf_(to_float(main_[(int64_t)t * ld + C + h]));
+}
+
+extern "C" int acorn_delta_prep(const void* main_, int64_t ld, const float* up, int64_t ld_up, const float* conv_w,
+                                const float* state, int64_t slot_stride, int64_t conv_off, const float* A_log,
+                                const float* dt_bias, const int* token_row, const int* row_start, const int* row_slot,
+                                float* qn, float* kn, float* vv, float* beta, float* g, float* gate, int tokens, int H,
+                                int KH, int dim, int vdim, int taps, int dtype, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    const int64_t C = 2 * (int64_t)KH * dim + (int64_t)H * vdim;
+    if (KH < 1 || KH > 64 || H % KH || taps < 1 || taps > DELTA_MAX_TAPS || C * 4 > 160 * 1024) return ACORN_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)C * sizeof(float);
+    if (smem > 48 * 1024) {
+        static AcornPerDevice configured;
+        if (!configured.seen()) {
+            cudaError_t e = cudaFuncSetAttribute(delta_prep_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(delta_prep_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+            if (e != cudaSuccess) return (int)e;
+            configured.mark();
+        }
+    }
+    ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(delta_prep_kernel<T>, dim3(tokens), dim3(256), smem, stream,
+                                                       (const T*)main_, ld, up, ld_up, conv_w, state, slot_stride, conv_off,
+                                                       A_log, dt_bias, token_row, row_start, row_slot, qn, kn, vv, beta, g,
+                                                       gate, H, KH, dim, vdim, taps));
+    return ACORN_ERR_UNSUPPORTED;
+}
+
+// The convolution's memory after the step: the last taps - 1 inputs of the request, i.e. of the old
+// memory followed by the row's inputs.  A thread owns a channel of a row, reads what it needs and
+// only then writes, so a row shorter than the memory shifts it correctly.
+template <typename T>
+__global__ void conv_state_update_kernel(const T* __restrict__ main_, int64_t ld, float* __restrict__ state,
+                                         int64_t slot_stride, int64_t conv_off, const int* __restrict__ row_start,
+                                         const int* __restrict__ row_slot, int C, int taps) {
+    pdl_wait();
+    pdl_trigger();
+    const int r = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int first = row_start[r], L = row_start[r + 1] - first;
+    float* cs = state + (int64_t)row_slot[r] * slot_stride + conv_off;
+    float keep[DELTA_MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < DELTA_MAX_TAPS - 1; ++j) {
+        if (j < taps - 1) {
+            const int idx = L + j - (taps - 1);         // index into the row's inputs; negative: old memory
+            keep[j] = idx >= 0 ? to_float(main_[(int64_t)(first + idx) * ld + c]) : cs[(int64_t)(L + j) * C + c];
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < DELTA_MAX_TAPS - 1; ++j)
+        if (j < taps - 1) cs[(int64_t)j * C + c] = keep[j];
+}
+
+extern "C" int acorn_conv_state_update(const void* main_, int64_t ld, float* state, int64_t slot_stride, int64_t conv_off,
+                                       const int* row_start, const int* row_slot, int rows, int C, int taps, int dtype,
+                                       cudaStream_t stream) {
+    if (rows <= 0 || taps <= 1) return 0;
+    if (taps > DELTA_MAX_TAPS || rows > 65535) return ACORN_ERR_UNSUPPORTED;
+    dim3 grid((C + 127) / 128, rows);
+    ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(conv_state_update_kernel<T>, grid, dim3(128), 0, stream,
+                                                       (const T*)main_, ld, state, slot_stride, conv_off, row_start,
+                                                       row_slot, C, taps));
+    return ACORN_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------- the recurrence
+// A block: one row, one head, 32 value channels.  Thread (column, slice): the state entries S[d, column]
+// for d = slice, slice + 4, ... (DPT of them, in registers).  The four slices of a column sit in
+// neighbouring lanes and add their partial dot products by two shuffles.  The tokens' q, k, g (dim
+// values each) and v, beta are staged through shared memory, DELTA_STAGE tokens at a time.
+#define DELTA_COLS 32
+#define DELTA_SLICES 4
+#define DELTA_STAGE 8
+
+template <int DPT>
+__global__ void __launch_bounds__(DELTA_COLS * DELTA_SLICES) delta_rule_kernel(
+    const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vv,
+    const float* __restrict__ beta, const float* __restrict__ g, float* __restrict__ state, int64_t slot_stride,
+    const int* __restrict__ row_start, const int* __restrict__ row_slot, float* __restrict__ out, int H, int KH, int dim,
+    int vdim) {
+    extern __shared__ float sm[];                       // [STAGE][3][dim] q, k, g; then [STAGE][COLS] v; [STAGE] beta
+    pdl_wait();
+    pdl_trigger();
+    const int r = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * DELTA_COLS;
+    const int kh = h / (H / KH);
+    const int slice = threadIdx.x & (DELTA_SLICES - 1), col = threadIdx.x / DELTA_SLICES;
+    const int column = c0 + col;
+    const bool live = column < vdim;
+    float* S_g = state + (int64_t)row_slot[r] * slot_stride + (int64_t)h * dim * vdim;
+    float S[DPT];
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+        const int d = slice + DELTA_SLICES * i;
+        S[i] = (live && d < dim) ? S_g[(int64_t)d * vdim + column] : 0.f;
+    }
+    float* sq = sm;
+    float* sv = sm + DELTA_STAGE * 3 * dim;
+    float* sb = sv + DELTA_STAGE * DELTA_COLS;
+    const int first = row_start[r], last = row_start[r + 1];
+    for (int t0 = first; t0 < last; t0 += DELTA_STAGE) {
+        const int n = min(DELTA_STAGE, last - t0);
+        __syncthreads();
+        for (int e = threadIdx.x; e < n * dim; e += blockDim.x) {
+            const int tt = e / dim, d = e % dim;
+            const int64_t t = t0 + tt;
+            sq[(tt * 3 + 0) * dim + d] = qn[(t * KH + kh) * dim + d];
+            sq[(tt * 3 + 1) * dim + d] = kn[(t * KH + kh) * dim + d];
+            sq[(tt * 3 + 2) * dim + d] = g[(t * H + h) * dim + d];
+        }
+        for (int e = threadIdx.x; e < n * DELTA_COLS; e += blockDim.x) {
+            const int tt = e / DELTA_COLS, cc = e % DELTA_COLS;
+            sv[e] = (c0 + cc < vdim) ? vv[((int64_t)(t0 + tt) * H + h) * vdim + c0 + cc] : 0.f;
+        }
+        if (threadIdx.x < n) sb[threadIdx.x] = beta[(int64_t)(t0 + threadIdx.x) * H + h];
+        __syncthreads();
+        for (int tt = 0; tt < n; ++tt) {
+            const float* q = sq + (tt * 3 + 0) * dim;
+            const float* k = sq + (tt * 3 + 1) * dim;
+            const float* gg = sq + (tt * 3 + 2) * dim;
+            float dot = 0.f;
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) {
+                const int d = slice + DELTA_SLICES * i;
+                if (d < dim) {
+                    S[i] *= gg[d];
+                    dot = fmaf(S[i], k[d], dot);
+                }
+            }
+            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+            const float u = sb[tt] * (sv[tt * DELTA_COLS + col] - dot);
+            float o = 0.f;
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) {
+                const int d = slice + DELTA_SLICES * i;
+                if (d < dim) {
+                    S[i] = fmaf(k[d], u, S[i]);
+                    o = fmaf(S[i], q[d], o);
+                }
+            }
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            if (slice == 0 && live) out[((int64_t)(t0 + tt) * H + h) * vdim + column] = o;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+        const int d = slice + DELTA_SLICES * i;
+        if (live && d < dim) S_g[(int64_t)d * vdim + column] = S[i];
+    }
+}
+
+extern "C" int acorn_delta_rule(const float* qn, const float* kn, const float* vv, const float* beta, const float* g,
+                                float* state, int64_t slot_stride, const int* row_start, const int* row_slot, float* out,
+                                int rows, int H, int KH, int dim, int vdim, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (H > 65535 || (vdim + DELTA_COLS - 1) / DELTA_COLS > 65535 || dim > 256 || H % KH) return ACORN_ERR_UNSUPPORTED;
+    dim3 grid(rows, H, (vdim + DELTA_COLS - 1) / DELTA_COLS);
+    dim3 block(DELTA_COLS * DELTA_SLICES);
+    const size_t smem = (size_t)(DELTA_STAGE * 3 * dim + DELTA_STAGE * DELTA_COLS + DELTA_STAGE) * sizeof(float);
+#define DELTA_LAUNCH(N) return acorn_launch(delta_rule_kernel<N>, grid, block, smem, stream, qn, kn, vv, beta, g, state, \
+                                            slot_stride, row_start, row_slot, out, H, KH, dim, vdim)
+    if (dim <= 32) DELTA_LAUNCH(8);
+    if (dim <= 64) DELTA_LAUNCH(16);
+    if (dim <= 128) DELTA_LAUNCH(32);
+    DELTA_LAUNCH(64);
+#undef DELTA_LAUNCH
+}
+
+// y[t, h, :] = o / sqrt(mean(o^2) + eps) * w * gate   (w [vdim] shared by the heads)
+template <typename T>
+__global__ void delta_out_kernel(const float* __restrict__ o, const float* __restrict__ gate, const float* __restrict__ w,
+                                 T* __restrict__ y, int vdim, float eps, int64_t total_heads) {
+    pdl_wait();
+    pdl_trigger();
+    const int lane = threadIdx.x & 31;
+    const int64_t th = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);     // token * H + head
+    if (th >= total_heads) return;
+    const float* row = o + th * vdim;
+    float ss = 0.f;
+    for (int j = lane; j < vdim; j += 32) ss += row[j] * row[j];
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)vdim + eps);
+    for (int j = lane; j < vdim; j += 32) y[th * vdim + j] = from_float<T>(row[j] * inv * w[j] * gate[th * vdim + j]);
+}
+
+extern "C" int acorn_delta_out(const float* o, const float* gate, const float* w, void* y, int tokens, int H, int vdim,
+                               float eps, int dtype, cudaStream_t stream) {
+    const int64_t total = (int64_t)tokens * H;
+    if (total <= 0) return 0;
+    const int64_t blocks = (total + 3) / 4;
+    if (blocks > 0x7fffffff) return ACORN_ERR_UNSUPPORTED;
+    ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(delta_out_kernel<T>, dim3((unsigned)blocks), dim3(128), 0, stream, o,
+                                                       gate, w, (T*)y, vdim, eps, total));
+    return ACORN_ERR_UNSUPPORTED;
+}

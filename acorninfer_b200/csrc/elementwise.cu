@@ -234,3 +234,85 @@ extern "C" int acorn_cast(const void* in, void* out, int64_t n, int dtype_in, in
         return ACORN_ERR_UNSUPPORTED;
     return acorn_launch_status();
 }
+
+// ---------------------------------------------------------------- hashed bigram rows
+// resid32[t] += table[row(t)]: row = (prev * mul_prev + cur * mul_cur) mod buckets, where prev is the token
+// before t in its request; a request's first token takes row `buckets`.  The token before a row's
+// first token is the request's state (prev_state[slot], the last token of its previous step); the block
+// of a row's first token reads it and then stores the row's last token there.
+template <typename T>
+__global__ void bigram_add_kernel(float* __restrict__ resid32, const int* __restrict__ token_ids,
+                                  const int* __restrict__ token_row, const int* __restrict__ row_start,
+                                  const int* __restrict__ row_pos, const int* __restrict__ row_slot,
+                                  int* __restrict__ prev_state, const T* __restrict__ table, int H, int buckets,
+                                  int mul_prev, int mul_cur) {
+    __shared__ int s_row;
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x;
+    if (threadIdx.x == 0) {
+        const int r = token_row[t], first = row_start[r];
+        const int cur = token_ids[t];
+        int row;
+        if (t > first) {
+            row = (int)(((int64_t)token_ids[t - 1] * mul_prev + (int64_t)cur * mul_cur) % buckets);
+        } else {
+            const int slot = row_slot[r];
+            row = row_pos[r] == 0 ? buckets
+                                  : (int)(((int64_t)prev_state[slot] * mul_prev + (int64_t)cur * mul_cur) % buckets);
+            prev_state[slot] = token_ids[row_start[r + 1] - 1];
+        }
+        s_row = row;
+    }
+    __syncthreads();
+    const T* src = table + (int64_t)s_row * H;
+    float* o = resid32 + (int64_t)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] += to_float(src[i]);
+}
+
+extern "C" int acorn_bigram_add(float* resid32, const int* token_ids, const int* token_row, const int* row_start,
+                                const int* row_pos, const int* row_slot, int* prev_state, const void* table,
+                                int tokens, int H, int buckets, int mul_prev, int mul_cur, int dtype,
+                                cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (buckets < 1) return ACORN_ERR_UNSUPPORTED;
+    ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(bigram_add_kernel<T>, dim3(tokens), dim3(128), 0, stream, resid32,
+                                                       token_ids, token_row, row_start, row_pos, row_slot, prev_state,
+                                                       (const T*)table, H, buckets, mul_prev, mul_cur));
+    return ACORN_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------- RMSNorm of a sublayer's output, added
+// resid32[t] += y[t] * rsqrt(mean(y[t]^2) + eps) * w   (float32), and, if `rounded` is given, the new
+// residual row rounded to T: what the next sublayer reads.
+template <typename T>
+__global__ void rmsnorm_add_kernel(float* __restrict__ resid32, const T* __restrict__ y, const float* __restrict__ w,
+                                   T* __restrict__ rounded, int H, float eps) {
+    __shared__ float scratch[32];
+    pdl_wait();
+    pdl_trigger();
+    const int64_t row = blockIdx.x;
+    const T* yr = y + row * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = to_float(yr[i]);
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    float* x = resid32 + row * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = x[i] + to_float(yr[i]) * inv * w[i];
+        x[i] = v;
+        if (rounded) rounded[row * H + i] = from_float<T>(v);
+    }
+}
+
+extern "C" int acorn_rmsnorm_add(float* resid32, const void* y, const float* w, void* rounded, int rows, int H,
+                                 float eps, int dtype, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(rmsnorm_add_kernel<T>, dim3(rows), dim3(threads), 0, stream, resid32,
+                                                       (const T*)y, w, (T*)rounded, H, eps));
+    return ACORN_ERR_UNSUPPORTED;
+}

@@ -98,7 +98,29 @@ class _Sigs:
                         c_int, c_void_p]
     acorn_attention_plain = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
-                             c_void_p]
+                             c_int, c_void_p, c_void_p]
+    acorn_bigram_add = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                        c_int, c_int, c_int, c_int, c_void_p]
+    acorn_rmsnorm_add = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]
+    acorn_latent_prep = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
+                         c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                         c_int, c_void_p]
+    acorn_head_linear = [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int,
+                         c_int, c_void_p]
+    acorn_delta_prep = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p,
+                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+    acorn_conv_state_update = [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int, c_int,
+                               c_int, c_void_p]
+    acorn_delta_rule = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
+                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
+    acorn_delta_out = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p]
+    acorn_moe_route = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
+    acorn_moe_plan = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    acorn_grouped_gemm = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_int,
+                          c_int, c_int, c_void_p]
+    acorn_moe_combine = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                         c_void_p]
     acorn_attention_decode = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                               c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                               c_int, c_void_p, c_void_p, c_void_p]
@@ -398,9 +420,19 @@ def qk_rope_kv(qkv: torch.Tensor, q_weight32: torch.Tensor | None, k_weight32: t
 def attention_plain(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pages: torch.Tensor,
                     block_table: torch.Tensor, page_base: torch.Tensor, token_row: torch.Tensor,
                     positions: torch.Tensor, num_tokens: int, num_heads: int, num_kv_heads: int, head_dim: int,
-                    scale: float, window: int | None, out: torch.Tensor | None = None) -> torch.Tensor:
+                    scale: float, window: int | None, out: torch.Tensor | None = None,
+                    value_dim: int | None = None, sink32: torch.Tensor | None = None) -> torch.Tensor:
     """Paged causal attention for any mix of rows; ``q`` may be the head of a wider buffer
-    (row stride ``q_stride`` elements).  Returns [tokens, nq * d]."""
+    (row stride ``q_stride`` elements).  Returns [tokens, nq * value_dim].  ``value_dim`` (default
+    ``head_dim``): the leading entries of a value row that are summed; ``v_pages`` may be ``k_pages``
+    itself.  ``sink32`` (float32 [nq]): a learned term exp(sink) per query head in the softmax denominator."""
+    dv = head_dim if value_dim is None else int(value_dim)
+    if not (1 <= dv <= head_dim):
+        raise KernelError(f"value_dim must be in 1..head_dim, got {dv}")
+    if sink32 is not None:
+        _check(sink32, "sink", torch.float32, 1)
+        if sink32.numel() != num_heads:
+            raise KernelError("sink must have one entry per query head")
     if head_dim > 512:
         raise KernelError(f"plain attention supports head_dim <= 512, got {head_dim}")
     if num_heads % num_kv_heads:
@@ -409,13 +441,13 @@ def attention_plain(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pag
     _check(v_pages, "v_pages", q.dtype, 4)
     _check(block_table, "block_table", torch.int32, 2)
     if out is None:
-        out = torch.empty((num_tokens, num_heads * head_dim), dtype=q.dtype, device=q.device)
+        out = torch.empty((num_tokens, num_heads * dv), dtype=q.dtype, device=q.device)
     _check(out, "out", q.dtype, 2)
     _ok(lib().acorn_attention_plain(q.data_ptr(), q_stride, out.data_ptr(), k_pages.data_ptr(),
                                     v_pages.data_ptr(), block_table.data_ptr(), page_base.data_ptr(),
                                     block_table.stride(0), token_row.data_ptr(), positions.data_ptr(),
                                     num_tokens, num_heads, num_kv_heads, head_dim, k_pages.shape[2],
-                                    float(scale), int(window or 0), dtype_code(q.dtype), _stream()),
+                                    float(scale), int(window or 0), dtype_code(q.dtype), dv, _ptr(sink32), _stream()),
         "attention_plain")
     return out
 
@@ -940,6 +972,229 @@ def linear(x, w: torch.Tensor, out_dtype: torch.dtype | None = None, epilogue: A
         if _TIMER is not None:
             _TIMER.end("library_gemm", f"{x.shape[0]}x{w.shape[0]}x{x.shape[1]}")
 
+
+
+# ------------------------------------------------------------------ hashed bigram rows, output norms
+
+
+def bigram_add(resid32: torch.Tensor, token_ids: torch.Tensor, token_row: torch.Tensor, row_start: torch.Tensor,
+               row_pos: torch.Tensor, row_slot: torch.Tensor, prev_state: torch.Tensor, table: torch.Tensor,
+               buckets: int, mul_prev: int, mul_cur: int) -> torch.Tensor:
+    """resid32[t] += table[(prev * mul_prev + cur * mul_cur) mod buckets], row ``buckets`` for a request's
+    first token.  ``prev_state`` (int32 [slots]) holds every request's last token between steps and is
+    updated."""
+    _check(resid32, "resid32", torch.float32, 2)
+    _check(table, "table", None, 2)
+    _check(prev_state, "prev_state", torch.int32, 1)
+    for t, n in ((token_ids, "token_ids"), (token_row, "token_row"), (row_start, "row_start"), (row_pos, "row_pos"),
+                 (row_slot, "row_slot")):
+        _check(t, n, torch.int32, 1)
+    T, H = resid32.shape
+    if table.shape != (buckets + 1, H):
+        raise KernelError(f"bigram table {tuple(table.shape)} is not [buckets + 1, width] = [{buckets + 1}, {H}]")
+    _ok(lib().acorn_bigram_add(resid32.data_ptr(), token_ids.data_ptr(), token_row.data_ptr(), row_start.data_ptr(),
+                               row_pos.data_ptr(), row_slot.data_ptr(), prev_state.data_ptr(), table.data_ptr(), T, H,
+                               int(buckets), int(mul_prev), int(mul_cur), dtype_code(table.dtype), _stream()), "bigram_add")
+    return resid32
+
+
+class RoundedRows:
+    """The residual stream as the next sublayer reads it (rounded to the activation dtype; the float32
+    stream itself under a float32 engine), with nothing left to add: what a block hands on when it has
+    already added its last result."""
+
+    def __init__(self, x: torch.Tensor):
+        self.x = x
+
+
+def rmsnorm_add(resid32: torch.Tensor, y: torch.Tensor, weight32: torch.Tensor, eps: float,
+                rounded: bool = True) -> torch.Tensor | None:
+    """resid32 += rmsnorm(y) * weight (in place, float32).  Returns the new residual rows rounded to
+    ``y``'s dtype if that is not float32 and ``rounded`` is set (else None)."""
+    _check(resid32, "resid32", torch.float32, 2)
+    _check(y, "y", None, 2)
+    _check(weight32, "weight", torch.float32, 1)
+    if y.shape != resid32.shape or weight32.numel() != y.shape[1]:
+        raise KernelError(f"rmsnorm_add: y {tuple(y.shape)}, residual {tuple(resid32.shape)}, weight {weight32.numel()}")
+    out = torch.empty_like(y) if (rounded and y.dtype != torch.float32) else None
+    _ok(lib().acorn_rmsnorm_add(resid32.data_ptr(), y.data_ptr(), weight32.data_ptr(), _ptr(out), y.shape[0], y.shape[1],
+                                float(eps), dtype_code(y.dtype), _stream()), "rmsnorm_add")
+    return out
+
+
+# ------------------------------------------------------------------ attention through a latent
+
+
+def latent_prep(proj: torch.Tensor, qcat: torch.Tensor, c_weight32: torch.Tensor | None, inv_freq: torch.Tensor,
+                magnitude: float, positions: torch.Tensor, token_row: torch.Tensor, block_table: torch.Tensor,
+                page_base: torch.Tensor, pages: torch.Tensor | None, num_heads: int, dim: int, rot: int, rank: int,
+                rot_dims: int, eps: float) -> None:
+    """Rotates the rotated part of every head's query into ``qcat[t, h, rank:]`` and, with ``pages``
+    ([pages, 1, P, rank + rot]), writes the token's cache row: the RMS-normed latent and the rotated
+    shared key part.  ``proj`` [T, H (dim + rot) (+ rank + rot)]."""
+    _check(proj, "proj", None, 2)
+    _check(qcat, "qcat", proj.dtype, 3)
+    T = proj.shape[0]
+    write = pages is not None
+    want = num_heads * (dim + rot) + (rank + rot if write else 0)
+    if proj.shape[1] != want or qcat.shape != (T, num_heads, rank + rot):
+        raise KernelError(f"latent_prep: proj {tuple(proj.shape)} / qcat {tuple(qcat.shape)} do not fit H={num_heads}, "
+                          f"dim={dim}, rot={rot}, rank={rank}")
+    _check(inv_freq, "inv_freq", torch.float32, 1)
+    if inv_freq.numel() != rot_dims // 2:
+        raise KernelError("inv_freq must have rot_dims / 2 entries")
+    P = 1
+    if write:
+        _check(pages, "pages", proj.dtype, 4)
+        _check(c_weight32, "latent norm weight", torch.float32, 1)
+        if pages.shape[1] != 1 or pages.shape[3] != rank + rot or c_weight32.numel() != rank:
+            raise KernelError(f"latent_prep: cache pages {tuple(pages.shape)} do not fit rank + rot = {rank + rot}")
+        P = pages.shape[2]
+    _ok(lib().acorn_latent_prep(proj.data_ptr(), proj.stride(0), qcat.data_ptr(), _ptr(c_weight32), inv_freq.data_ptr(),
+                                float(magnitude), positions.data_ptr(), token_row.data_ptr(), block_table.data_ptr(),
+                                page_base.data_ptr(), block_table.stride(0), _ptr(pages), T, num_heads, dim, rot, rank,
+                                rot_dims, P, float(eps), 1 if write else 0, dtype_code(proj.dtype), _stream()), "latent_prep")
+
+
+def head_linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    """y[t, h, :] = w[h] x[t, h, :] for every head.  x [T, H, I] and y [T, H, O] may be views with any
+    token and head strides (innermost contiguous); w [H, O, I] contiguous."""
+    _check(w, "w", x.dtype, 3)
+    H, O, I = w.shape
+    if x.dim() != 3 or y.dim() != 3 or x.shape[1:] != (H, I) or y.shape != (x.shape[0], H, O) or y.dtype != x.dtype:
+        raise KernelError(f"head_linear: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)} do not fit")
+    if x.stride(2) != 1 or y.stride(2) != 1 or not x.is_cuda or not y.is_cuda:
+        raise KernelError("head_linear: innermost dimensions must be contiguous CUDA memory")
+    _ok(lib().acorn_head_linear(x.data_ptr(), x.stride(0), x.stride(1), w.data_ptr(), y.data_ptr(), y.stride(0), y.stride(1),
+                                x.shape[0], H, O, I, dtype_code(x.dtype), _stream()), "head_linear", f"{x.shape[0]}x{H}x{O}x{I}")
+    return y
+
+
+# ------------------------------------------------------------------ gated delta rule
+
+
+def delta_prep(main: torch.Tensor, up32: torch.Tensor, conv_w32: torch.Tensor, state: torch.Tensor, conv_off: int,
+               a_log32: torch.Tensor, dt_bias32: torch.Tensor, token_row: torch.Tensor, row_start: torch.Tensor,
+               row_slot: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int, taps: int):
+    """Convolution + silu of the q, k, v channels, unit norms, write strength, decays and output gate of
+    every token: returns float32 (q [T, KH, dim], k [T, KH, dim], v [T, H, vdim], beta [T, H],
+    g [T, H, dim], gate [T, H, vdim])."""
+    _check(main, "main", None, 2)
+    _check(up32, "up", torch.float32, 2)
+    _check(state, "state", torch.float32, 2)
+    _check(conv_w32, "conv weights", torch.float32, 2)
+    T = main.shape[0]
+    C = 2 * kv_heads * dim + heads * vdim
+    if main.shape[1] != C + heads or up32.shape != (T, heads * dim + heads * vdim) or conv_w32.shape != (C, taps):
+        raise KernelError(f"delta_prep: main {tuple(main.shape)}, up {tuple(up32.shape)}, conv {tuple(conv_w32.shape)} do not fit")
+    if state.shape[1] < conv_off + (taps - 1) * C or a_log32.numel() != heads or dt_bias32.numel() != heads * dim:
+        raise KernelError("delta_prep: state or decay parameters do not fit")
+    dev = main.device
+    f = lambda *shape: torch.empty(shape, dtype=torch.float32, device=dev)
+    q, k, v = f(T, kv_heads, dim), f(T, kv_heads, dim), f(T, heads, vdim)
+    beta, g, gate = f(T, heads), f(T, heads, dim), f(T, heads, vdim)
+    _ok(lib().acorn_delta_prep(main.data_ptr(), main.stride(0), up32.data_ptr(), up32.stride(0), conv_w32.data_ptr(),
+                               state.data_ptr(), state.stride(0), int(conv_off), a_log32.data_ptr(), dt_bias32.data_ptr(),
+                               token_row.data_ptr(), row_start.data_ptr(), row_slot.data_ptr(), q.data_ptr(), k.data_ptr(),
+                               v.data_ptr(), beta.data_ptr(), g.data_ptr(), gate.data_ptr(), T, heads, kv_heads, dim, vdim,
+                               taps, dtype_code(main.dtype), _stream()), "delta_prep")
+    return q, k, v, beta, g, gate
+
+
+def conv_state_update(main: torch.Tensor, state: torch.Tensor, conv_off: int, row_start: torch.Tensor,
+                      row_slot: torch.Tensor, num_rows: int, channels: int, taps: int) -> None:
+    """The last ``taps - 1`` convolution inputs of every row's request into its state."""
+    _ok(lib().acorn_conv_state_update(main.data_ptr(), main.stride(0), state.data_ptr(), state.stride(0), int(conv_off),
+                                      row_start.data_ptr(), row_slot.data_ptr(), num_rows, channels, taps,
+                                      dtype_code(main.dtype), _stream()), "conv_state_update")
+
+
+def delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, g: torch.Tensor,
+               state: torch.Tensor, row_start: torch.Tensor, row_slot: torch.Tensor, num_rows: int) -> torch.Tensor:
+    """The recurrence over every row's tokens from the state in its slot (updated in place): float32
+    o [T, H, vdim]."""
+    T, H, vdim = v.shape
+    KH, dim = q.shape[1], q.shape[2]
+    for t, n in ((q, "q"), (k, "k"), (v, "v"), (beta, "beta"), (g, "g")):
+        _check(t, n, torch.float32)
+    _check(state, "state", torch.float32, 2)
+    if state.shape[1] < H * dim * vdim or g.shape != (T, H, dim) or dim > 256:
+        raise KernelError(f"delta_rule: sizes do not fit (state {tuple(state.shape)}, H={H}, dim={dim}, vdim={vdim})")
+    out = torch.empty((T, H, vdim), dtype=torch.float32, device=v.device)
+    _ok(lib().acorn_delta_rule(q.data_ptr(), k.data_ptr(), v.data_ptr(), beta.data_ptr(), g.data_ptr(), state.data_ptr(),
+                               state.stride(0), row_start.data_ptr(), row_slot.data_ptr(), out.data_ptr(), num_rows, H, KH,
+                               dim, vdim, _stream()), "delta_rule")
+    return out
+
+
+def delta_out(o32: torch.Tensor, gate32: torch.Tensor, weight32: torch.Tensor, eps: float, dtype: torch.dtype) -> torch.Tensor:
+    """Per token and head o / rms(o) * weight * gate -> [T, H * vdim] in ``dtype``."""
+    T, H, vdim = o32.shape
+    _check(o32, "o", torch.float32, 3)
+    _check(gate32, "gate", torch.float32, 3)
+    _check(weight32, "weight", torch.float32, 1)
+    y = torch.empty((T, H * vdim), dtype=dtype, device=o32.device)
+    _ok(lib().acorn_delta_out(o32.data_ptr(), gate32.data_ptr(), weight32.data_ptr(), y.data_ptr(), T, H, vdim, float(eps),
+                              dtype_code(dtype), _stream()), "delta_out")
+    return y
+
+
+# ------------------------------------------------------------------ routed experts
+
+
+def moe_route(z32: torch.Tensor, correction32: torch.Tensor, top: int, groups: int, keep: int):
+    """(chosen [T, top] int32, weights [T, top] float32) from router logits z [T, N]."""
+    _check(z32, "router logits", torch.float32, 2)
+    _check(correction32, "correction", torch.float32, 1)
+    T, N = z32.shape
+    if correction32.numel() != N:
+        raise KernelError("moe_route: correction must have one entry per router output")
+    idx = torch.empty((T, top), dtype=torch.int32, device=z32.device)
+    wts = torch.empty((T, top), dtype=torch.float32, device=z32.device)
+    _ok(lib().acorn_moe_route(z32.data_ptr(), correction32.data_ptr(), idx.data_ptr(), wts.data_ptr(), T, N, int(top),
+                              int(groups), int(keep), _stream()), "moe_route")
+    return idx, wts
+
+
+def moe_plan(idx: torch.Tensor, num_outputs: int):
+    """Groups the (token, choice) pairs by chosen output: (offsets [N + 1], slot_of [T, top], slot_token
+    [T * top]), all int32."""
+    _check(idx, "idx", torch.int32, 2)
+    T, top = idx.shape
+    dev = idx.device
+    offsets = torch.empty(num_outputs + 1, dtype=torch.int32, device=dev)
+    slot_of = torch.empty((T, top), dtype=torch.int32, device=dev)
+    slot_token = torch.empty(T * top, dtype=torch.int32, device=dev)
+    _ok(lib().acorn_moe_plan(idx.data_ptr(), offsets.data_ptr(), slot_of.data_ptr(), slot_token.data_ptr(), T * top,
+                             num_outputs, top, _stream()), "moe_plan")
+    return offsets, slot_of, slot_token
+
+
+def grouped_gemm(a: torch.Tensor, a_rows: torch.Tensor | None, w: torch.Tensor, offsets: torch.Tensor, slots: int) -> torch.Tensor:
+    """out[slot] = a[a_rows[slot]] @ w[e]^T for the slots offsets[e] .. offsets[e + 1] - 1 of every
+    expert e (w [E, N, K]); rows of other slots are left unwritten."""
+    _check(a, "a", None, 2)
+    _check(w, "w", a.dtype, 3)
+    E, N, K = w.shape
+    if a.shape[1] != K:
+        raise KernelError(f"grouped_gemm: a {tuple(a.shape)} against w {tuple(w.shape)}")
+    out = torch.empty((slots, N), dtype=a.dtype, device=a.device)
+    _ok(lib().acorn_grouped_gemm(a.data_ptr(), a.stride(0), _ptr(a_rows), w.data_ptr(), out.data_ptr(), out.stride(0),
+                                 offsets.data_ptr(), slots, E, N, K, dtype_code(a.dtype), _stream()), "grouped_gemm",
+        f"{slots}x{N}x{K}")
+    return out
+
+
+def moe_combine(y: torch.Tensor, x: torch.Tensor, slot_of: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor,
+                num_experts: int) -> torch.Tensor:
+    """out[t] = sum_k wts[t, k] * (idx[t, k] >= num_experts ? x[t] : y[slot_of[t, k]])."""
+    _check(y, "y", x.dtype, 2)
+    _check(x, "x", None, 2)
+    T, H = x.shape
+    out = torch.empty_like(x)
+    _ok(lib().acorn_moe_combine(y.data_ptr(), x.data_ptr(), slot_of.data_ptr(), idx.data_ptr(), wts.data_ptr(), out.data_ptr(),
+                                T, H, idx.shape[1], int(num_experts), dtype_code(x.dtype), _stream()), "moe_combine")
+    return out
 
 # ------------------------------------------------------------------ sampling
 

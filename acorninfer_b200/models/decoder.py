@@ -46,13 +46,14 @@ class Decoder:
         self._named_parts: list[tuple[str, object]] = []     # (prefix, part) for tensor collection
         for ls in spec.layers:
             mixer = build_part(MIXERS, ls.mixer, self.ctx)
-            ff = build_part(FEED_FORWARDS, ls.feed_forward, self.ctx)
+            ff = build_part(FEED_FORWARDS, ls.feed_forward, self.ctx) if ls.feed_forward is not None else None
             norms = {k: build_part(NORMS, v, self.ctx) for k, v in ls.norms.items()}
             block = BLOCKS.get(ls.block.kind)(ctx=self.ctx, mixer=mixer, feed_forward=ff, norms=norms,
                                               **ls.block.params)
             self.blocks.append(block)
             self._named_parts.append((ls.mixer.prefix, mixer))
-            self._named_parts.append((ls.feed_forward.prefix, ff))
+            if ff is not None:
+                self._named_parts.append((ls.feed_forward.prefix, ff))
             for k, v in ls.norms.items():
                 self._named_parts.append((v.prefix, norms[k]))
             self._named_parts.append((ls.block.prefix, block))
@@ -99,21 +100,31 @@ class Decoder:
     # ------------------------------------------------------------------ cache needs
 
     def cache_needs(self) -> tuple[dict[int, KVNeeds], dict[int, StateNeeds]]:
-        """Per schedule entry that keeps something: its KV needs and its state needs."""
+        """Per schedule entry that keeps something: its KV needs and its state needs.  An entry whose
+        pages other runs read keeps them for the widest window among its readers and itself.  Stages
+        that keep state per request appear under their own keys (``"<where>.<index>"``)."""
+        from dataclasses import replace
         kv: dict[int, KVNeeds] = {}
-        state: dict[int, StateNeeds] = {}
+        state: dict = {}
         for i, e in enumerate(self.spec.schedule):
             needs = self.blocks[e.layer].mixer.cache_needs()
             if e.reads_cache_of is not None:
-                owner = self.blocks[self.spec.schedule[e.reads_cache_of].layer].mixer.cache_needs()
-                if needs.kv is None or owner.kv is None or needs.kv.group_key != owner.kv.group_key:
+                owner = kv.get(e.reads_cache_of)
+                if needs.kv is None or owner is None or needs.kv.layout_key != owner.layout_key:
                     raise ValueError(f"schedule entry {i} cannot read the cache of entry {e.reads_cache_of}: "
                                      "their mixers keep different things")
+                if owner.window is not None and (needs.kv.window is None or needs.kv.window > owner.window):
+                    kv[e.reads_cache_of] = replace(owner, window=needs.kv.window)
                 continue
             if needs.kv is not None:
                 kv[i] = needs.kv
             if needs.state is not None:
                 state[i] = needs.state
+        for where, stages in self.stages.items():
+            for n, st in enumerate(stages):
+                sn = st.state_needs()
+                if sn is not None:
+                    state[f"{where}.{n}"] = sn
         return kv, state
 
     def entry_caches(self, manager) -> list[EntryCache]:
@@ -126,6 +137,10 @@ class Decoder:
             else:
                 k = v = group = None
             out.append(EntryCache(i, group, k, v, e.reads_cache_of is None, manager.state.get(i)))
+        for where, stages in self.stages.items():
+            for n, st in enumerate(stages):
+                if f"{where}.{n}" in manager.state:
+                    st.state = manager.state[f"{where}.{n}"]
         return out
 
     def step_arrays(self) -> dict:
@@ -157,6 +172,8 @@ class Decoder:
             resid32, delta = self.blocks[e.layer].forward(resid32, delta, inputs, caches[i], next_norm=nxt)
         if inputs.num_logits == 0:
             return None
+        if isinstance(delta, ops.RoundedRows):          # the last block already added its result
+            delta = None
         h = self.final_norm.add_forward(resid32, delta, rows=inputs.logit_tokens)
         for stage in self.stages["before_head"]:
             h = stage.forward(h, inputs)

@@ -37,7 +37,8 @@ class TensorSpec:
     """One checkpoint tensor a part expects.
 
     ``init`` tells the random-weights mode how to fill it: ``"matrix"`` N(0, sigma),
-    ``"norm"`` 1 + N(0, sigma_norm), ``"table"`` integers.
+    ``"norm"`` 1 + N(0, sigma_norm), ``"table"`` integers.  A ``None`` in ``shape`` is a size that
+    the checkpoint decides (the loader accepts any; the random-weights mode needs it given).
     """
 
     shape: tuple[int, ...]
@@ -56,11 +57,12 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: the arrangement (``block``) and the parts it arranges."""
+    """One layer: the arrangement (``block``) and the parts it arranges.  ``feed_forward`` None: a
+    layer of a mixer alone (the arrangement must allow it)."""
 
     block: PartSpec
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: PartSpec | None
     norms: dict[str, PartSpec]
 
 
@@ -106,16 +108,23 @@ class BuildContext:
 class KVNeeds:
     """Keys and values in pages.  ``window`` None: every earlier key is read;
     an integer w: a query at position p reads keys p-w+1 .. p.  ``dtype`` None: the engine's
-    activation dtype."""
+    activation dtype.  ``values`` False: one row per token and kv head only (a mixer whose values are
+    a function of its key rows, such as attention through a cached latent)."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
     dtype: torch.dtype | None = None
+    values: bool = True
 
     @property
     def group_key(self) -> tuple:
-        return ("kv", self.num_kv_heads, self.head_dim, self.window, self.dtype)
+        return ("kv", self.num_kv_heads, self.head_dim, self.window, self.dtype, self.values)
+
+    @property
+    def layout_key(self) -> tuple:
+        """What two runs must agree on for one to read the other's pages (their windows may differ)."""
+        return (self.num_kv_heads, self.head_dim, self.dtype, self.values)
 
 
 @dataclass(frozen=True)
@@ -223,7 +232,15 @@ class Stage(Part):
     """A step of the model outside its layers: a scale or learned positions added after the token
     table, a transform of the final hidden rows, a cap on the logits.  ``forward(x, inputs) -> x``
     (it may work in place); where it stands says what ``x`` is (``ModelSpec.after_embedding``,
-    ``before_head``, ``after_head``)."""
+    ``before_head``, ``after_head``).  A stage that keeps something per request between steps (the
+    token before a step's first one, say) returns ``StateNeeds`` from ``state_needs()`` and finds the
+    tensor ``[slots, *shape]`` in ``self.state`` (a request's row is ``inputs.row_slot``; zeroed
+    when a request takes the slot)."""
+
+    state = None
+
+    def state_needs(self) -> "StateNeeds | None":
+        return None
 
     def forward(self, x: torch.Tensor, inputs: "Any") -> torch.Tensor:
         raise NotImplementedError

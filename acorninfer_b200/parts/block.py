@@ -4,9 +4,16 @@
 (``Qwen3Block`` in ``acorninfer/models/qwen3.py:399-410``).  The residual stream is float32;
 each sum is fused into the norm that follows it, so a block takes ``(resid32, delta)``
 where ``delta`` is what the previous block still has to add, and returns the same pair.
+
+``outnorm``: ``x += norm_m(mixer(x)); x += norm_f(feed_forward(x))``: the sublayers read the
+stream itself and only their outputs are normed (Kogonex).  The sums are done here, in float32, by
+the kernel that norms the output; it also hands on the stream rounded to the activation dtype, which
+is what the next sublayer reads (``RoundedRows``).  A layer may have no feed-forward.
 """
 
 from __future__ import annotations
+
+import torch
 
 from ..kernels import ops
 from .base import BLOCKS, Block
@@ -33,6 +40,8 @@ class PreNormBlock(Block):
         # With few rows on the tensor-core path, each residual sum and the norm after it are done
         # by the product before them (no kernel of their own); otherwise by the fused norm kernel.
         fuse = self._fuses(inputs.num_tokens)
+        if isinstance(delta, ops.RoundedRows):          # the block before added its result itself
+            delta = None
         h = delta if isinstance(delta, ops.NormedRows) else self.norms["mixer"].add_forward(resid32, delta)
         ep = self.norms["feed_forward"].as_epilogue(resid32) if fuse else None
         if ep is not None:
@@ -50,3 +59,34 @@ class PreNormBlock(Block):
         if self.feed_forward.adds_residual:
             return resid32, self.feed_forward.forward(h, inputs, residual32=resid32)
         return resid32, self.feed_forward.forward(h, inputs)
+
+
+@BLOCKS.register("outnorm")
+class OutputNormBlock(Block):
+    graph_safe = True
+
+    def __init__(self, ctx, mixer, feed_forward, norms):
+        super().__init__(mixer, feed_forward, norms)
+        self.ctx = ctx
+        want = {"mixer"} | ({"feed_forward"} if feed_forward is not None else set())
+        if want - set(norms):
+            raise ValueError(f"outnorm block needs norms named {sorted(want)}; missing {sorted(want - set(norms))}")
+
+    def _rows(self, resid32, rounded):
+        if self.ctx.dtype == torch.float32:
+            return resid32
+        return rounded if rounded is not None else ops.cast(resid32, self.ctx.dtype)
+
+    def forward(self, resid32, delta, inputs, cache, next_norm=None):
+        if isinstance(delta, ops.RoundedRows):
+            h = self._rows(resid32, delta.x)
+        else:
+            if isinstance(delta, ops.NormedRows):
+                raise ValueError("an outnorm block cannot follow a block that fused the next norm into its last product")
+            if delta is not None:
+                resid32.add_(delta)
+            h = self._rows(resid32, None)
+        h = self._rows(resid32, self.norms["mixer"].normed_add(resid32, self.mixer.forward(h, inputs, cache)))
+        if self.feed_forward is not None:
+            h = self._rows(resid32, self.norms["feed_forward"].normed_add(resid32, self.feed_forward.forward(h, inputs)))
+        return resid32, ops.RoundedRows(h)

@@ -1,0 +1,101 @@
+"""Attention whose keys and values are up-projections of one cached latent per token, as a mixer.
+
+Per token: ``q = W_q h`` laid out head by head as [dim unrotated | rot rotated]; ``W_dkv h`` gives
+``kv_rank`` entries that are RMS-normed into the latent ``c`` and ``rot`` entries that are rotated into
+one key part ``kr`` shared by all heads.  Head a's key is ``[U_a c | kr]``, its value ``V_a c``
+(``U_a``: rows a*dim.. of ``uk``, ``V_a``: rows a*vdim.. of ``uv``).  Only ``[c | kr]`` is cached: one
+row of ``kv_rank + rot`` per token, no separate values.  Since ``qu . U_a c = (U_a^T qu) . c``, every
+head attends over those rows directly with the query ``[U_a^T qu_a | qr_a]`` and gets
+``sum_j p_j c_j``, which ``V_a`` maps to the head's output: one kv head of size ``kv_rank + rot`` whose
+value rows are the first ``kv_rank`` entries of its key rows.  A sliding window and a learned sink per
+head (a term exp(sink_a) in the softmax denominator, with no key and no value) are the attention
+kernel's; ``scale`` multiplies the whole score.
+
+A run that reads another run's cache (``cache.write`` false) has no ``dkv`` matrices: it computes
+queries only, against the rows the other run wrote, with its own up-projections, window and sinks.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from .base import MIXERS, BuildContext, CacheNeeds, KVNeeds, Mixer, TensorSpec
+
+
+@MIXERS.register("latent_attention")
+class LatentAttention(Mixer):
+    graph_safe = True
+
+    def __init__(self, ctx: BuildContext, hidden_size: int, num_heads: int, dim: int, rot_dim: int, vdim: int,
+                 kv_rank: int, scale: float, norm_eps: float, position: str | None, window: int | None = None,
+                 own_cache: bool = True):
+        if window is not None and window < 1:
+            raise ValueError(f"window must be >= 1 or None, got {window}")
+        self.ctx = ctx
+        self.hidden_size = hidden_size
+        self.H, self.dim, self.rot, self.vdim, self.rank = num_heads, dim, rot_dim, vdim, kv_rank
+        self.scale, self.eps, self.window, self.own_cache = float(scale), float(norm_eps), window, own_cache
+        self.position = ctx.positions[position] if position is not None else None
+        if self.position is not None and self.position.head_dim != rot_dim:
+            raise ValueError("position encoding was built for another rotated size")
+        self.w_in = self.w_uk_t = self.w_uv = self.w_o = self.c_norm32 = self.sink32 = None
+
+    def tensor_specs(self):
+        H, qd = self.H, self.dim + self.rot
+        specs = {
+            "q": TensorSpec((H * qd, self.hidden_size)),
+            "uk": TensorSpec((H * self.dim, self.rank)),
+            "uv": TensorSpec((H * self.vdim, self.rank)),
+            "sink": TensorSpec((H,), "sink"),
+            "o": TensorSpec((self.hidden_size, H * self.vdim)),
+        }
+        if self.own_cache:
+            specs["dkv"] = TensorSpec((self.rank + self.rot, self.hidden_size))
+            specs["dkv.norm"] = TensorSpec((self.rank,), "norm")
+        return specs
+
+    def bind(self, tensors):
+        parts = [tensors["q"]] + ([tensors["dkv"]] if self.own_cache else [])
+        dtype = parts[0].dtype if all(p.dtype == parts[0].dtype for p in parts) else torch.float32
+        self.w_in = torch.cat([p.to(dtype) for p in parts], dim=0).contiguous()
+        # U_a^T per head: [H, rank, dim], so that the query side is a per-head product like the value side
+        self.w_uk_t = tensors["uk"].view(self.H, self.dim, self.rank).transpose(1, 2).contiguous()
+        self.w_uv = tensors["uv"].view(self.H, self.vdim, self.rank).contiguous()
+        self.w_o = tensors["o"].contiguous()
+        self.sink32 = tensors["sink"].to(torch.float32).contiguous()
+        if self.own_cache:
+            self.c_norm32 = tensors["dkv.norm"].to(torch.float32).contiguous()
+
+    def cache_needs(self):
+        return CacheNeeds(kv=KVNeeds(1, self.rank + self.rot, self.window, values=False))
+
+    def forward(self, x, inputs, cache):
+        if cache.write != self.own_cache:
+            raise ValueError("latent attention: the schedule and the layer disagree on who writes the cache")
+        g = inputs.groups[cache.group]
+        T, H, dt = x.shape[0], self.H, self.ctx.dtype
+        pos = self.position
+        proj = ops.linear(x, self.w_in, out_dtype=dt)
+        qcat = torch.empty((T, H, self.rank + self.rot), dtype=dt, device=x.device)
+        ops.latent_prep(proj, qcat, self.c_norm32, pos.inv_freq if pos is not None else _no_freq(x.device),
+                        pos.magnitude if pos is not None else 1.0, inputs.positions, inputs.token_row, g.block_table,
+                        g.page_base, cache.k_pages if cache.write else None, H, self.dim, self.rot, self.rank,
+                        pos.rotary_dim if pos is not None else 0, self.eps)
+        qu = proj[:, :H * (self.dim + self.rot)].view(T, H, self.dim + self.rot)[:, :, :self.dim]
+        ops.head_linear(qu, self.w_uk_t.to(dt) if self.w_uk_t.dtype != dt else self.w_uk_t, qcat[:, :, :self.rank])
+        o = ops.attention_plain(qcat, qcat.stride(0), cache.k_pages, cache.k_pages, g.block_table, g.page_base,
+                                inputs.token_row, inputs.positions, T, H, 1, self.rank + self.rot, self.scale,
+                                self.window, value_dim=self.rank, sink32=self.sink32)
+        v = torch.empty((T, H, self.vdim), dtype=dt, device=x.device)
+        ops.head_linear(o.view(T, H, self.rank), self.w_uv, v)
+        return ops.linear(v.view(T, H * self.vdim), self.w_o, out_dtype=dt)
+
+
+_NO_FREQ: dict = {}
+
+
+def _no_freq(device):
+    if device not in _NO_FREQ:
+        _NO_FREQ[device] = torch.zeros(0, dtype=torch.float32, device=device)
+    return _NO_FREQ[device]

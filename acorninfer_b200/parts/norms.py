@@ -18,18 +18,27 @@ from .base import NORMS, BuildContext, Norm, TensorSpec
 class RMSNorm(Norm):
     graph_safe = True
 
-    def __init__(self, ctx: BuildContext, width: int, eps: float):
+    def __init__(self, ctx: BuildContext, width: int, eps: float, tensor: str = "weight"):
+        """``tensor``: the weight's name relative to the part's prefix ("" where the prefix is the
+        whole name)."""
         self.ctx = ctx
         self.width = width
         self.eps = float(eps)
+        self.tensor = tensor
         self.weight32: torch.Tensor | None = None
 
     def tensor_specs(self):
-        return {"weight": TensorSpec((self.width,), "norm")}
+        return {self.tensor: TensorSpec((self.width,), "norm")}
 
     def bind(self, tensors):
         # Norm weights are held in float32 whatever they were stored as (widening is exact).
-        self.weight32 = tensors["weight"].to(torch.float32).contiguous()
+        self.weight32 = tensors[self.tensor].to(torch.float32).contiguous()
+
+    def normed_add(self, resid32, y, rounded=True):
+        """resid32 += norm(y) (in place): the norm of a sublayer's *output*, added to the stream.
+        Returns the new stream rounded to the activation dtype (None under a float32 engine, where the
+        stream itself is read, or if ``rounded`` is off)."""
+        return ops.rmsnorm_add(resid32, y, self.weight32, self.eps, rounded=rounded)
 
     def as_epilogue(self, resid32):
         return ops.AddNormEpilogue(resid32, self.weight32, self.eps)

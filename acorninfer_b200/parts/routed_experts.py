@@ -1,0 +1,72 @@
+"""A routed mixture of small SwiGLU experts, some of which are the identity, as a feed-forward.
+
+Router logits ``z = W_router h`` over ``experts + identity`` outputs, in float32; scores
+``s = softmax(z)``; the choice scores are ``s + correction``.  The outputs form ``groups`` equal groups
+of neighbours, a group's score is its largest choice score, and only outputs of the ``keep`` best groups
+can be chosen (the others count as minus infinity).  The ``top`` largest choice scores win; their
+weights are ``s`` itself, not renormalized.  The last ``identity`` outputs are identity experts: no
+tensors, output = input.  A real expert is ``down(silu(gate h) * (up h))``.  The result is the weighted
+sum over the chosen.
+
+On the device: the router's choice (one kernel), the (token, choice) pairs grouped by expert (one
+kernel), one product per expert over its own rows for gate/up and for down (a kernel each, walking
+the per-expert offsets on the device: nothing of the routing is read on the host), SwiGLU, and the
+weighted sum in the order of the choices.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from .base import FEED_FORWARDS, BuildContext, FeedForward, TensorSpec
+
+
+@FEED_FORWARDS.register("routed_experts")
+class RoutedExperts(FeedForward):
+    graph_safe = True
+
+    def __init__(self, ctx: BuildContext, hidden_size: int, expert_size: int, num_experts: int, num_identity: int,
+                 top: int, groups: int = 1, keep: int = 1):
+        n = num_experts + num_identity
+        if n < 1 or n % groups or not (1 <= keep <= groups) or top > keep * (n // groups):
+            raise ValueError(f"{n} router outputs do not split into {groups} groups of which {keep} hold {top} choices")
+        self.ctx = ctx
+        self.hidden_size, self.ff = hidden_size, expert_size
+        self.E, self.I, self.top, self.groups, self.keep = num_experts, num_identity, top, groups, keep
+        self.w_router32 = self.correction32 = self.w_gate_up = self.w_down = None
+
+    def tensor_specs(self):
+        n = self.E + self.I
+        specs = {"router": TensorSpec((n, self.hidden_size)), "correction": TensorSpec((n,), "bias")}
+        for e in range(self.E):
+            specs[f"e{e}.gate"] = TensorSpec((self.ff, self.hidden_size))
+            specs[f"e{e}.up"] = TensorSpec((self.ff, self.hidden_size))
+            specs[f"e{e}.down"] = TensorSpec((self.hidden_size, self.ff))
+        return specs
+
+    def bind(self, tensors):
+        t = tensors
+        self.w_router32 = t["router"].to(torch.float32).contiguous()
+        self.correction32 = t["correction"].to(torch.float32).contiguous()
+        if self.E:
+            mats = [t[f"e{e}.{n}"] for e in range(self.E) for n in ("gate", "up", "down")]
+            dtype = mats[0].dtype if all(m.dtype == mats[0].dtype for m in mats) else torch.float32
+            self.w_gate_up = torch.stack([torch.cat([t[f"e{e}.gate"].to(dtype), t[f"e{e}.up"].to(dtype)], dim=0)
+                                          for e in range(self.E)]).contiguous()               # [E, 2 ff, width]
+            self.w_down = torch.stack([t[f"e{e}.down"].to(dtype) for e in range(self.E)]).contiguous()   # [E, width, ff]
+
+    def forward(self, x, inputs):
+        T = x.shape[0]
+        z = ops.linear(x, self.w_router32, out_dtype=torch.float32)
+        idx, wts = ops.moe_route(z, self.correction32, self.top, self.groups, self.keep)
+        offsets, slot_of, slot_token = ops.moe_plan(idx, self.E + self.I)
+        slots = T * self.top
+        if self.E:
+            w_gu = self.w_gate_up if self.w_gate_up.dtype == x.dtype else self.w_gate_up.to(x.dtype)
+            w_dn = self.w_down if self.w_down.dtype == x.dtype else self.w_down.to(x.dtype)
+            hidden = ops.swiglu(ops.grouped_gemm(x, slot_token, w_gu, offsets, slots))
+            y = ops.grouped_gemm(hidden, None, w_dn, offsets, slots)
+        else:
+            y = x
+        return ops.moe_combine(y, x, slot_of, idx, wts, self.E)

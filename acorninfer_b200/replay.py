@@ -33,6 +33,7 @@ def parse_args(argv=None):
     p.add_argument("--max-tokens", type=int, required=True,
                    help="most tokens live requests hold at any time (each rounded up to 64)")
     p.add_argument("--page-size", type=int, default=16, help="tokens per cache page (divides 64)")
+    p.add_argument("--max-requests", type=int, default=4, help="state slots: the most requests live at any time")
     p.add_argument("--device", default="cuda:0")
     return p.parse_args(argv)
 
@@ -53,7 +54,7 @@ def main(argv=None) -> int:
     num_blocks = -(-args.max_tokens // args.page_size)
     runner = ModelRunner.from_model_dir(
         args.model, dtype=args.dtype, device=args.device, num_blocks=num_blocks, page_size=args.page_size,
-        max_requests=16, max_step_tokens=max(args.max_tokens, 64))
+        max_requests=args.max_requests, max_step_tokens=max(args.max_tokens, 64))
     session = TraceSession(runner)
     for line in sys.stdin:
         line = line.strip()

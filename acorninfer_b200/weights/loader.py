@@ -39,8 +39,11 @@ def check_names_and_shapes(expected: dict[str, TensorSpec], found: dict[str, tup
     ignorable = set(ignorable)
     missing = [n for n, s in expected.items() if n not in found and not s.optional]
     unexpected = [n for n in found if n not in expected and n not in ignorable]
+    def fits(got, want):
+        return len(got) == len(want) and all(w is None or g == w for g, w in zip(got, want))
+
     wrong = [(n, found[n], expected[n].shape) for n in expected
-             if n in found and tuple(found[n]) != tuple(expected[n].shape)]
+             if n in found and not fits(tuple(found[n]), tuple(expected[n].shape))]
     if not (missing or unexpected or wrong):
         return
     lines = [f"{where or 'weights'}: tensors do not match the model"]

@@ -163,12 +163,19 @@ INIT_KINDS = Registry("init kind")
 INIT_KINDS.register("matrix", lambda d: d.normal(d.sigma))
 INIT_KINDS.register("norm", lambda d: d.normal(d.sigma_norm, 1.0))
 INIT_KINDS.register("table", lambda d: d.integers())
+# small parameters of recurrent and routed parts: values that keep every branch alive under random weights
+INIT_KINDS.register("bias", lambda d: d.normal(0.5))                   # additive terms: N(0, 0.5)
+INIT_KINDS.register("sink", lambda d: d.normal(1.0))                   # a softmax sink per head: N(0, 1)
+INIT_KINDS.register("conv", lambda d: d.normal(0.5, 1.0 / d.shape[-1]))        # taps around an average
+INIT_KINDS.register("decay_log", lambda d: d.normal(0.5, -1.0))        # log of a decay rate: exp(.) around 0.4
 
 
 def random_tensor(name: str, spec: TensorSpec, seed: int, sigma: float, sigma_norm: float,
                   dtype: torch.dtype, device: torch.device | str = "cpu", rows: tuple[int, int] | None = None,
                   backend: str | None = None) -> torch.Tensor:
     """The tensor ``name`` of the model with this seed (or rows ``rows[0]..rows[1]-1`` of it)."""
+    if any(n is None for n in spec.shape):
+        raise ValueError(f"tensor '{name}' has a size that only a checkpoint fixes ({spec.shape}): give it in the configuration")
     return INIT_KINDS.get(spec.init)(Draw(name, tuple(spec.shape), seed, sigma, sigma_norm, dtype,
                                           torch.device(device), rows, backend))
 
