@@ -31,7 +31,7 @@ __global__ void __launch_bounds__(PLAIN_THREADS) attention_plain_kernel(
     const T* __restrict__ q, int64_t q_stride, T* __restrict__ out, const T* __restrict__ k_pages,
     const T* __restrict__ v_pages, const int* __restrict__ block_table, const int* __restrict__ page_base,
     int table_stride, const int* __restrict__ token_row, const int* __restrict__ positions, int nq, int nkv, int d,
-    int P, float scale, int window, int parts, int dv, const float* __restrict__ sink) {
+    int P, float scale, int window, int parts, int dv, const float* __restrict__ sink, int hpb) {
     extern __shared__ __align__(16) float smem[];
     float* qs = smem;                                   // [heads][d], scaled
     float* sc = smem + PLAIN_HEADS * d;                 // [heads][PLAIN_THREADS] probabilities of the chunk
@@ -45,8 +45,8 @@ __global__ void __launch_bounds__(PLAIN_THREADS) attention_plain_kernel(
     const int t = blockIdx.x;
     const int rep = nq / nkv;
     const int kvh = blockIdx.y / parts, part = blockIdx.y % parts;
-    const int h0 = kvh * rep + part * PLAIN_HEADS;
-    const int G = min(PLAIN_HEADS, rep - part * PLAIN_HEADS);
+    const int h0 = kvh * rep + part * hpb;                 // hpb <= PLAIN_HEADS query heads a block
+    const int G = min(hpb, rep - part * hpb);
     const int r = token_row[t], pos = positions[t];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int* table = block_table + (int64_t)r * table_stride - page_base[r];
@@ -237,7 +237,12 @@ extern "C" int acorn_attention_plain(const void* q, int64_t q_stride, void* out,
     if (tokens <= 0) return 0;
     if (dv < 1 || dv > d) return ACORN_ERR_UNSUPPORTED;
     if (d < 1 || d > PLAIN_MAX_D || nkv < 1 || nq % nkv != 0) return ACORN_ERR_UNSUPPORTED;
-    const int parts = (nq / nkv + PLAIN_HEADS - 1) / PLAIN_HEADS;
+    // Eight query heads of a kv head share a block (a key row is fetched once for all of them) unless that
+    // leaves most of the device idle (few tokens, few kv heads): then fewer heads a block.  A head's
+    // result does not depend on how many share its block.
+    int hpb = PLAIN_HEADS;
+    while (hpb > 1 && (int64_t)tokens * nkv * ((nq / nkv + hpb - 1) / hpb) < 2 * 148) hpb /= 2;
+    const int parts = (nq / nkv + hpb - 1) / hpb;
     if ((int64_t)nkv * parts > 65535) return ACORN_ERR_UNSUPPORTED;
     // queries and probabilities (at most 32 KB), then the warps' hand-over buffers (40 KB)
     const size_t smem = (size_t)PLAIN_HEADS * (d + PLAIN_THREADS) * sizeof(float) + (size_t)PLAIN_WARPS * 32 * 5 * 16;
@@ -252,6 +257,6 @@ extern "C" int acorn_attention_plain(const void* q, int64_t q_stride, void* out,
     dim3 grid(tokens, nkv * parts);
     ACORN_DISPATCH_DTYPE(dtype, T, (attention_plain_kernel<T><<<grid, PLAIN_THREADS, smem, stream>>>(
         (const T*)q, q_stride, (T*)out, (const T*)k_pages, (const T*)v_pages, block_table, page_base,
-        table_stride, token_row, positions, nq, nkv, d, P, scale, window, parts, dv, sink)));
+        table_stride, token_row, positions, nq, nkv, d, P, scale, window, parts, dv, sink, hpb)));
     return acorn_launch_status();
 }

@@ -10,7 +10,7 @@
 //   grouped_gemm  C[slot, :] = A[row(slot), :] W_e^T for the slots of every expert e < E
 //   moe_combine   out[t] = sum_k weight_k * (chosen_k >= E ? x[t] : y[slot_of(t, k)])
 //                 (router outputs from E on are identity experts: they return their input)
-#include "common.cuh"
+#include "mma_helpers.cuh"
 
 // One warp per token.  Ties go to the lower index.
 __global__ void moe_route_kernel(const float* __restrict__ z, const float* __restrict__ correction,
@@ -238,9 +238,164 @@ __global__ void __launch_bounds__(256) grouped_gemm_kernel(const T* __restrict__
     }
 }
 
+// ---------------------------------------------------------------- the same on the tensor cores (bfloat16)
+// mma.sync m16n8k16, float32 accumulation in the order of K.  A block: BM slots of one expert by 128
+// weight rows; eight warps; operand tiles of 64 along K through a ring of cp.async stages.  BM = 64
+// (warps 2 x 4, 32 x 32 each) for steps with many rows an expert, BM = 16 (warps 1 x 8, 16 x 16 each) for
+// decode steps, where the kernel is bound by reading every chosen expert's matrix once.  An output
+// element is the same chain of products in both, so a row's bits do not depend on the step it is in.
+#define GT_BN 128
+#define GT_BK 64
+#define GT_LDS (GT_BK + 8)
+#define GT_STAGES 3
+
+template <int BM>
+__global__ void __launch_bounds__(256) grouped_gemm_tc_kernel(const bf16* __restrict__ A, int64_t lda,
+                                                              const int* __restrict__ a_rows, const bf16* __restrict__ W,
+                                                              bf16* __restrict__ C, int64_t ldc,
+                                                              const int* __restrict__ offsets, int E, int N, int K) {
+    extern __shared__ __align__(16) unsigned char gt_smem[];
+    bf16* sA = reinterpret_cast<bf16*>(gt_smem);                               // [STAGES][BM][LDS]
+    bf16* sW = sA + GT_STAGES * BM * GT_LDS;                                   // [STAGES][BN][LDS]
+    __shared__ int s_e, s_first, s_end;
+    __shared__ int64_t s_row[BM];
+    pdl_wait();
+    pdl_trigger();
+    if (threadIdx.x == 0) {
+        int tile = blockIdx.y, e = 0, found = -1;
+        for (; e < E; ++e) {
+            const int tiles = (offsets[e + 1] - offsets[e] + BM - 1) / BM;
+            if (tile < tiles) {
+                found = e;
+                break;
+            }
+            tile -= tiles;
+        }
+        s_e = found;
+        if (found >= 0) {
+            s_first = offsets[found] + tile * BM;
+            s_end = offsets[found + 1];
+        }
+    }
+    __syncthreads();
+    const int e = s_e;
+    if (e < 0) return;
+    const int first = s_first, end = s_end;
+    if (threadIdx.x < BM) {
+        const int slot = first + threadIdx.x;
+        s_row[threadIdx.x] = slot < end ? (a_rows ? (int64_t)a_rows[slot] : (int64_t)slot) : -1;
+    }
+    __syncthreads();
+    const int n0 = blockIdx.x * GT_BN;
+    const bf16* We = W + (int64_t)e * N * K;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr int WM = BM == 64 ? 2 : 1;                 // warps along the slots
+    constexpr int WN = 8 / WM;                           // warps along the weight rows
+    constexpr int MT = BM / WM / 16;                     // 16-row tiles a warp
+    constexpr int NT = GT_BN / WN / 8;                   // 8-column tiles a warp
+    const int wm = warp / WN, wn = warp % WN;
+    float acc[MT][NT][4] = {};
+    const int ktiles = (K + GT_BK - 1) / GT_BK;
+
+    auto load = [&](int kt, int stage) {
+        const int k0 = kt * GT_BK;
+        bf16* a = sA + stage * BM * GT_LDS;
+        bf16* w = sW + stage * GT_BN * GT_LDS;
+        for (int i = threadIdx.x; i < BM * (GT_BK / 8); i += 256) {
+            const int r = i / (GT_BK / 8), seg = i % (GT_BK / 8);
+            const int k = k0 + seg * 8;
+            const bool ok = s_row[r] >= 0 && k < K;
+            cp_async_16(smem_addr(a + r * GT_LDS + seg * 8), ok ? A + s_row[r] * lda + k : A, ok);
+        }
+        for (int i = threadIdx.x; i < GT_BN * (GT_BK / 8); i += 256) {
+            const int r = i / (GT_BK / 8), seg = i % (GT_BK / 8);
+            const int k = k0 + seg * 8, n = n0 + r;
+            const bool ok = n < N && k < K;
+            cp_async_16(smem_addr(w + r * GT_LDS + seg * 8), ok ? We + (int64_t)n * K + k : We, ok);
+        }
+    };
+
+#pragma unroll
+    for (int st = 0; st < GT_STAGES - 1; ++st) {
+        if (st < ktiles) load(st, st);
+        cp_async_commit();
+    }
+    for (int kt = 0; kt < ktiles; ++kt) {
+        cp_async_wait<GT_STAGES - 2>();
+        __syncthreads();
+        if (kt + GT_STAGES - 1 < ktiles) load(kt + GT_STAGES - 1, (kt + GT_STAGES - 1) % GT_STAGES);
+        cp_async_commit();
+        const bf16* a = sA + (kt % GT_STAGES) * BM * GT_LDS;
+        const bf16* w = sW + (kt % GT_STAGES) * GT_BN * GT_LDS;
+#pragma unroll
+        for (int kk = 0; kk < GT_BK; kk += 16) {
+            uint32_t af[MT][4];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                const int row = wm * (BM / WM) + mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                ldmatrix_x4(af[mt], smem_addr(a + row * GT_LDS + kk + (lane >> 4) * 8));
+            }
+#pragma unroll
+            for (int np = 0; np < NT / 2; ++np) {
+                uint32_t bfr[4];
+                const int row = wn * (GT_BN / WN) + np * 16 + (lane & 7) + (lane >> 4) * 8;
+                ldmatrix_x4(bfr, smem_addr(w + row * GT_LDS + kk + ((lane >> 3) & 1) * 8));
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    mma_bf16_16816(acc[mt][2 * np], af[mt], bfr[0], bfr[1]);
+                    mma_bf16_16816(acc[mt][2 * np + 1], af[mt], bfr[2], bfr[3]);
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int slot = first + wm * (BM / WM) + mt * 16 + g + half * 8;
+            if (slot >= end) continue;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const int n = n0 + wn * (GT_BN / WN) + nt * 8 + 2 * t;
+                const float v0 = acc[mt][nt][half * 2], v1 = acc[mt][nt][half * 2 + 1];
+                if (n + 1 < N && (ldc & 1) == 0) {
+                    *reinterpret_cast<uint32_t*>(C + (int64_t)slot * ldc + n) = pack_bf16(v0, v1);
+                } else {
+                    if (n < N) C[(int64_t)slot * ldc + n] = __float2bfloat16_rn(v0);
+                    if (n + 1 < N) C[(int64_t)slot * ldc + n + 1] = __float2bfloat16_rn(v1);
+                }
+            }
+        }
+    }
+}
+
+template <int BM>
+static int grouped_gemm_tc_launch(const bf16* A, int64_t lda, const int* a_rows, const bf16* W, bf16* C, int64_t ldc,
+                                  const int* offsets, int slots, int E, int N, int K, cudaStream_t stream) {
+    const int64_t tiles = (slots + BM - 1) / BM + E;
+    if (tiles > 65535) return ACORN_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)GT_STAGES * (BM + GT_BN) * GT_LDS * sizeof(bf16);
+    static AcornPerDevice configured;
+    if (!configured.seen()) {
+        cudaError_t err = cudaFuncSetAttribute(grouped_gemm_tc_kernel<BM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) return (int)err;
+        configured.mark();
+    }
+    dim3 grid((N + GT_BN - 1) / GT_BN, (unsigned)tiles);
+    return acorn_launch(grouped_gemm_tc_kernel<BM>, grid, dim3(256), smem, stream, A, lda, a_rows, W, C, ldc, offsets, E, N, K);
+}
+
 extern "C" int acorn_grouped_gemm(const void* A, int64_t lda, const int* a_rows, const void* W, void* C, int64_t ldc,
                                   const int* offsets, int slots, int E, int N, int K, int dtype, cudaStream_t stream) {
     if (slots <= 0 || E <= 0 || N <= 0) return 0;
+    if (dtype == ACORN_DTYPE_BF16 && K % 8 == 0 && lda % 8 == 0 && ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0) {
+        // few rows an expert on average: the small tile (a decode step); else the large one
+        if ((int64_t)slots <= (int64_t)16 * E)
+            return grouped_gemm_tc_launch<16>((const bf16*)A, lda, a_rows, (const bf16*)W, (bf16*)C, ldc, offsets, slots, E, N, K, stream);
+        return grouped_gemm_tc_launch<64>((const bf16*)A, lda, a_rows, (const bf16*)W, (bf16*)C, ldc, offsets, slots, E, N, K, stream);
+    }
     const int64_t tiles = (slots + GG_BM - 1) / GG_BM + E;       // every expert may end in a partly filled tile
     if (tiles > 65535) return ACORN_ERR_UNSUPPORTED;
     dim3 grid((N + GG_BN - 1) / GG_BN, (unsigned)tiles);

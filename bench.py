@@ -575,6 +575,143 @@ def reference_arm(args) -> int:
     return 0
 
 
+# ------------------------------------------------------------------ Kogonex beside Qwen3 at equal size
+
+KOGONEX_SIZES = {
+    # width, vocabulary, layers as (mixer kind, ...) patterns; all sizes of a layer as a real model has them
+    "w1024": dict(width=1024, vocab=32768, heads=8, dim=64, rot=32, vdim=64, rank=192, window=512,
+                  d_heads=8, d_kv_heads=4, d_dim=64, d_vdim=128, taps=4, decay_rank=32, gate_rank=64,
+                  ff=512, experts=14, identity=2, top=4, groups=4, keep=2),
+    "w2048": dict(width=2048, vocab=65536, heads=16, dim=128, rot=64, vdim=128, rank=384, window=1024,
+                  d_heads=16, d_kv_heads=8, d_dim=128, d_vdim=128, taps=4, decay_rank=64, gate_rank=128,
+                  ff=1024, experts=30, identity=2, top=6, groups=4, keep=2),
+}
+KOGONEX_PATTERN = ("delta", "latent", "delta", "delta", "shared")       # five layers, repeated
+
+
+def kogonex_config(z: dict, repeats: int):
+    from acorninfer_b200.config.model_config import (ChannelDeltaConfig, KogonexConfig, KogonexLayer, LatentAttentionConfig,
+                                                     RotaryScaling, RoutedExpertsConfig)
+    layers = []
+    moe = RoutedExpertsConfig(ff=z["ff"], experts=z["experts"], identity=z["identity"], top=z["top"], groups=z["groups"],
+                              keep=z["keep"])
+    for r in range(repeats):
+        for kind in KOGONEX_PATTERN:
+            if kind == "delta":
+                m = ChannelDeltaConfig(heads=z["d_heads"], kv_heads=z["d_kv_heads"], dim=z["d_dim"], vdim=z["d_vdim"],
+                                       conv=z["taps"], decay_rank=z["decay_rank"], gate_rank=z["gate_rank"])
+            else:
+                m = LatentAttentionConfig(heads=z["heads"], dim=z["dim"], rot_dim=z["rot"], vdim=z["vdim"], kv_rank=z["rank"],
+                                          scale=(z["dim"] + z["rot"]) ** -0.5, rot_dims=z["rot"], rot_base=1e6,
+                                          scaling=RotaryScaling(4.0, 4096, 32.0, 1.0), window=z["window"],
+                                          kv_from=(len(layers) - 3) if kind == "shared" else None)
+            layers.append(KogonexLayer(m, moe))
+    return KogonexConfig(vocab_size=z["vocab"], hidden_size=z["width"], norm_eps=1e-5, layers=tuple(layers),
+                         bigram_buckets=100003, bigram_mul_prev=1000003, bigram_mul_cur=31)
+
+
+def kernel_times(runner, entries_fn, torch) -> dict:
+    """Device time of every kernel of one step, each timed alone (``ops.kernel_timer``), summed by entry point."""
+    from acorninfer_b200.kernels import ops
+    was = runner.decode_graph
+    runner.decode_graph = False
+    try:
+        entries, done = entries_fn()
+        runner.step(entries)                 # warm
+        done()
+        entries, done = entries_fn()
+        torch.cuda.synchronize()
+        with ops.kernel_timer() as timer:
+            runner.step(entries)
+            rec = timer.records()
+        done()
+    finally:
+        runner.decode_graph = was
+    out: dict = {}
+    for what, tag, us in rec:
+        key = what if what not in ("library_gemm", "gemm_tc", "gemm_f32") else "products"
+        n, t = out.get(key, (0, 0.0))
+        out[key] = (n + 1, t + us)
+    return {k: {"launches": n, "us": round(t, 1)} for k, (n, t) in sorted(out.items(), key=lambda kv: -kv[1][1])}
+
+
+def design_bench(args) -> int:
+    """``--design kogonex``: prefill and decode of Kogonex at layer sizes of a real model (random weights), beside
+    Qwen3 dense of the same width, depth, vocabulary and active feed-forward width."""
+    import torch
+
+    from acorninfer_b200.config.model_config import Qwen3Config
+    from acorninfer_b200.engine.batch import StepEntry
+    from acorninfer_b200.engine.runner import ModelRunner
+
+    pk = peaks()
+    out = {"metric": "Kogonex beside Qwen3 dense at equal width, depth and active feed-forward width (1 B200)",
+           "unit": "tokens/s", "dtype": "bf16", "data": "synthetic", "impl": "ours", "n_gpus": 1, "steps": args.steps,
+           "warmup": args.warmup, "peaks": pk, "sizes": {}}
+    context, prompt = 2048, 2048
+    for name in (args.design_sizes.split(",") if args.design_sizes else list(KOGONEX_SIZES)):
+        z = KOGONEX_SIZES[name]
+        repeats = 2
+        models = {
+            "kogonex": kogonex_config(z, repeats),
+            "qwen3": Qwen3Config(num_hidden_layers=repeats * len(KOGONEX_PATTERN), hidden_size=z["width"],
+                                 num_attention_heads=z["heads"], num_key_value_heads=max(1, z["heads"] // 4), head_dim=128,
+                                 intermediate_size=z["top"] * z["ff"], rms_norm_eps=1e-6, rope_theta=1e6,
+                                 vocab_size=z["vocab"], tie_word_embeddings=False, bos_token_id=None, eos_token_id=()),
+        }
+        res = {}
+        for which, cfg in models.items():
+            max_b = 64
+            runner = ModelRunner.from_random(cfg, seed=1, sigma=0.02, dtype="bfloat16",
+                                             num_blocks=(max_b + 2) * (context + 64) // PAGE, page_size=PAGE,
+                                             max_requests=max_b + 2, max_step_tokens=4096)
+            for g in runner.manager.groups:
+                g.storage.normal_(0, 1)
+            r = {"prefill_ms": round(time_prefill(runner, prompt, 4, torch), 3)}
+            r["prefill_tok_s"] = round(prompt / (r["prefill_ms"] / 1e3), 1)
+            for b in (1, 8, 64):
+                d = time_decode(runner, None, b, args.steps, max(args.warmup, 3), context, torch)
+                r[f"decode_b{b}_tok_s"] = round(d["tok_s"], 1)
+                r[f"decode_b{b}_ms"] = round(d["ms_per_step"], 4)
+            gen = torch.Generator().manual_seed(3)
+
+            def prefill_entries():
+                rc = runner.open("kt_p")
+                toks = torch.randint(0, runner.vocab_size, (prompt,), generator=gen).tolist()
+                return [StepEntry(rc, toks, [prompt - 1])], (lambda: runner.close(rc))
+
+            def decode_entries():
+                reqs = synthetic_requests(runner, 8, context - 8, "kt_d")
+                return [StepEntry(rc, [5], [0]) for rc in reqs], (lambda: [runner.close(rc) for rc in reqs])
+
+            r["kernels_prefill_2048"] = kernel_times(runner, prefill_entries, torch)
+            r["kernels_decode_b8"] = kernel_times(runner, decode_entries, torch)
+            r["weight_gb"] = round(sum(t.numel() * t.element_size() for t in _model_tensors(runner)) / 1e9, 3)
+            res[which] = r
+            del runner
+            import gc
+            gc.collect()
+            torch.cuda.empty_cache()
+        out["sizes"][name] = res
+    out["value"] = out["sizes"][next(iter(out["sizes"]))]["kogonex"]["decode_b8_tok_s"]
+    print(json.dumps(out))
+    return 0
+
+
+def _model_tensors(runner):
+    seen, out = set(), []
+    for _, part in runner.decoder._named_parts:
+        for v in vars(part).values():
+            if hasattr(v, "data_ptr") and v.is_cuda and v.data_ptr() not in seen:
+                seen.add(v.data_ptr())
+                out.append(v)
+    for v in (runner.decoder.embedding, runner.decoder.head):
+        if v.data_ptr() not in seen:
+            seen.add(v.data_ptr())
+            out.append(v)
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -587,12 +724,17 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="only the batch of the headline value")
     ap.add_argument("--skip-extra", action="store_true",
                     help="leave out the per-kernel table, the continuous-batching, long-context and float32 runs")
+    ap.add_argument("--design", default=None, choices=["kogonex"],
+                    help="another workload: this design at layer sizes of a real model beside Qwen3 dense at equal size")
+    ap.add_argument("--design-sizes", default=None, help="with --design: comma-separated names of the size sets to run")
     args = ap.parse_args()
     if args.gpus != 1:
         print("bench.py: this engine runs on one GPU; --gpus must be 1")
         return 2
     if args.impl == "reference":
         return reference_arm(args)
+    if args.design is not None:
+        return design_bench(args)
     if args.warmup < 3:
         args.warmup = 3
 
