@@ -142,24 +142,41 @@ extern "C" int acorn_conv_state_update(const void* main_, int64_t ld, float* sta
 // ---------------------------------------------------------------- the recurrence
 // A block: one row, one head, 32 value channels.  Thread (column, slice): the state entries S[d, column]
 // for d = slice, slice + 4, ... (DPT of them, in registers).  The four slices of a column sit in
-// neighbouring lanes and add their partial dot products by two shuffles.  The tokens' q, k, g (dim
-// values each) and v, beta are staged through shared memory, DELTA_STAGE tokens at a time.
-#define DELTA_COLS 32
-#define DELTA_SLICES 4
-#define DELTA_STAGE 8
+// neighbouring lanes and add their partial dot products by two shuffles.
+//
+// What a token needs of S is one pass: with gk = g * k and gq = g * q (per key channel),
+//     a = sum_d S[d] gk[d]   (= (g S)^T k),      b = sum_d S[d] gq[d]   (= (g S)^T q),
+//     u = beta (v - a),      o = b + (k . q) u,    S[d] = g[d] S[d] + k[d] u,
+// so the two sums are reduced together and nothing is reduced after the update: the update of one
+// token overlaps the sums of the next.  The tokens' q, k, g, v, beta come through shared memory, `stage`
+// tokens at a time: the next stage's rows are fetched (cp.async) while this one is computed; gk, gq, g, k
+// are packed per channel into one 16-byte entry, and k . q is summed, once per stage.
+#define DELTA_THREADS 128
 
-template <int DPT>
-__global__ void __launch_bounds__(DELTA_COLS * DELTA_SLICES) delta_rule_kernel(
+__device__ __forceinline__ void cp_async_4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src));
+}
+
+template <int DPT, int DELTA_SLICES>
+__global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(
     const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vv,
     const float* __restrict__ beta, const float* __restrict__ g, float* __restrict__ state, int64_t slot_stride,
     const int* __restrict__ row_start, const int* __restrict__ row_slot, float* __restrict__ out, int H, int KH, int dim,
-    int vdim) {
-    extern __shared__ float sm[];                       // [STAGE][3][dim] q, k, g; then [STAGE][COLS] v; [STAGE] beta
+    int vdim, int stage) {
+    constexpr int DELTA_COLS = DELTA_THREADS / DELTA_SLICES;           // value channels a block
+    extern __shared__ __align__(16) float sm[];
+    constexpr int DIMP = DPT * DELTA_SLICES;                           // dim rounded up: entries beyond dim are zero
+    float4* pack = reinterpret_cast<float4*>(sm);                      // [stage][DIMP]: gk, gq, g, k
+    float* raw = sm + (size_t)stage * DIMP * 4;                        // [2][stage][3][dim] q, k, g as fetched
+    float* sv = raw + (size_t)2 * stage * 3 * dim;                     // [2][stage][COLS]
+    float* sb = sv + 2 * stage * DELTA_COLS;                           // [2][stage]
+    float* skq = sb + 2 * stage;                                       // [stage]
     pdl_wait();
     pdl_trigger();
     const int r = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * DELTA_COLS;
     const int kh = h / (H / KH);
     const int slice = threadIdx.x & (DELTA_SLICES - 1), col = threadIdx.x / DELTA_SLICES;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int column = c0 + col;
     const bool live = column < vdim;
     float* S_g = state + (int64_t)row_slot[r] * slot_stride + (int64_t)h * dim * vdim;
@@ -169,56 +186,85 @@ __global__ void __launch_bounds__(DELTA_COLS * DELTA_SLICES) delta_rule_kernel(
         const int d = slice + DELTA_SLICES * i;
         S[i] = (live && d < dim) ? S_g[(int64_t)d * vdim + column] : 0.f;
     }
-    float* sq = sm;
-    float* sv = sm + DELTA_STAGE * 3 * dim;
-    float* sb = sv + DELTA_STAGE * DELTA_COLS;
     const int first = row_start[r], last = row_start[r + 1];
-    for (int t0 = first; t0 < last; t0 += DELTA_STAGE) {
-        const int n = min(DELTA_STAGE, last - t0);
-        __syncthreads();
+    const int stages = (last - first + stage - 1) / stage;
+
+    auto fetch = [&](int s) {
+        const int t0 = first + s * stage, n = min(stage, last - t0);
+        float* rw = raw + (size_t)(s & 1) * stage * 3 * dim;
         for (int e = threadIdx.x; e < n * dim; e += blockDim.x) {
-            const int tt = e / dim, d = e % dim;
+            const int tt = e / dim, d = e - tt * dim;
             const int64_t t = t0 + tt;
-            sq[(tt * 3 + 0) * dim + d] = qn[(t * KH + kh) * dim + d];
-            sq[(tt * 3 + 1) * dim + d] = kn[(t * KH + kh) * dim + d];
-            sq[(tt * 3 + 2) * dim + d] = g[(t * H + h) * dim + d];
+            cp_async_4(rw + (tt * 3 + 0) * dim + d, qn + (t * KH + kh) * dim + d);
+            cp_async_4(rw + (tt * 3 + 1) * dim + d, kn + (t * KH + kh) * dim + d);
+            cp_async_4(rw + (tt * 3 + 2) * dim + d, g + (t * H + h) * dim + d);
         }
         for (int e = threadIdx.x; e < n * DELTA_COLS; e += blockDim.x) {
             const int tt = e / DELTA_COLS, cc = e % DELTA_COLS;
-            sv[e] = (c0 + cc < vdim) ? vv[((int64_t)(t0 + tt) * H + h) * vdim + c0 + cc] : 0.f;
+            float* dst = sv + ((s & 1) * stage + tt) * DELTA_COLS + cc;
+            if (c0 + cc < vdim) cp_async_4(dst, vv + ((int64_t)(t0 + tt) * H + h) * vdim + c0 + cc);
+            else *dst = 0.f;
         }
-        if (threadIdx.x < n) sb[threadIdx.x] = beta[(int64_t)(t0 + threadIdx.x) * H + h];
+        if (threadIdx.x < n) cp_async_4(sb + (s & 1) * stage + threadIdx.x, beta + (int64_t)(t0 + threadIdx.x) * H + h);
+    };
+
+    if (stages > 0) fetch(0);
+    asm volatile("cp.async.commit_group;\n" ::);
+    for (int s = 0; s < stages; ++s) {
+        if (s + 1 < stages) fetch(s + 1);
+        asm volatile("cp.async.commit_group;\n" ::);
+        asm volatile("cp.async.wait_group 1;\n" ::);
+        __syncthreads();                                               // stage s has arrived
+        const int t0 = first + s * stage, n = min(stage, last - t0);
+        const float* rw = raw + (size_t)(s & 1) * stage * 3 * dim;
+        for (int e = threadIdx.x; e < n * DIMP; e += blockDim.x) {
+            const int tt = e / DIMP, d = e % DIMP;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (d < dim) {
+                const float q = rw[(tt * 3 + 0) * dim + d], k = rw[(tt * 3 + 1) * dim + d], gg = rw[(tt * 3 + 2) * dim + d];
+                v = make_float4(gg * k, gg * q, gg, k);
+            }
+            pack[e] = v;
+        }
+        for (int tt = warp; tt < n; tt += DELTA_THREADS / 32) {
+            float kq = 0.f;
+            for (int d = lane; d < dim; d += 32) kq = fmaf(rw[(tt * 3 + 0) * dim + d], rw[(tt * 3 + 1) * dim + d], kq);
+            kq = warp_sum(kq);
+            if (lane == 0) skq[tt] = kq;
+        }
         __syncthreads();
+        const float* v_s = sv + (s & 1) * stage * DELTA_COLS;
+        const float* b_s = sb + (s & 1) * stage;
+        constexpr int UNROLL = DPT <= 16 ? 2 : 1;                      // (more would spill the state)
+#pragma unroll UNROLL
         for (int tt = 0; tt < n; ++tt) {
-            const float* q = sq + (tt * 3 + 0) * dim;
-            const float* k = sq + (tt * 3 + 1) * dim;
-            const float* gg = sq + (tt * 3 + 2) * dim;
-            float dot = 0.f;
+            const float4* p = pack + tt * DIMP + slice;                // this thread's channels: every fourth entry
+            float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+#pragma unroll
+            for (int i = 0; i < DPT; i += 2) {
+                const float4 e0 = p[DELTA_SLICES * i], e1 = p[DELTA_SLICES * (i + 1)];
+                a0 = fmaf(S[i], e0.x, a0);
+                b0 = fmaf(S[i], e0.y, b0);
+                a1 = fmaf(S[i + 1], e1.x, a1);
+                b1 = fmaf(S[i + 1], e1.y, b1);
+            }
+            float a = a0 + a1, b = b0 + b1;
+#pragma unroll
+            for (int o = 1; o < DELTA_SLICES; o <<= 1) {
+                a += __shfl_xor_sync(0xffffffffu, a, o);
+                b += __shfl_xor_sync(0xffffffffu, b, o);
+            }
+            const float u = b_s[tt] * (v_s[tt * DELTA_COLS + col] - a);
+            if (slice == 0 && live) out[((int64_t)(t0 + tt) * H + h) * vdim + column] = fmaf(skq[tt], u, b);
 #pragma unroll
             for (int i = 0; i < DPT; ++i) {
-                const int d = slice + DELTA_SLICES * i;
-                if (d < dim) {
-                    S[i] *= gg[d];
-                    dot = fmaf(S[i], k[d], dot);
-                }
+                const float4 e = p[DELTA_SLICES * i];
+                S[i] = fmaf(e.w, u, e.z * S[i]);
             }
-            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-            const float u = sb[tt] * (sv[tt * DELTA_COLS + col] - dot);
-            float o = 0.f;
-#pragma unroll
-            for (int i = 0; i < DPT; ++i) {
-                const int d = slice + DELTA_SLICES * i;
-                if (d < dim) {
-                    S[i] = fmaf(k[d], u, S[i]);
-                    o = fmaf(S[i], q[d], o);
-                }
-            }
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
-            if (slice == 0 && live) out[((int64_t)(t0 + tt) * H + h) * vdim + column] = o;
         }
+        __syncthreads();                                               // pack and this stage's rows are free again
     }
+    asm volatile("cp.async.wait_group 0;\n" ::);
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
         const int d = slice + DELTA_SLICES * i;
@@ -230,16 +276,29 @@ extern "C" int acorn_delta_rule(const float* qn, const float* kn, const float* v
                                 float* state, int64_t slot_stride, const int* row_start, const int* row_slot, float* out,
                                 int rows, int H, int KH, int dim, int vdim, cudaStream_t stream) {
     if (rows <= 0) return 0;
-    if (H > 65535 || (vdim + DELTA_COLS - 1) / DELTA_COLS > 65535 || dim > 256 || H % KH) return ACORN_ERR_UNSUPPORTED;
-    dim3 grid(rows, H, (vdim + DELTA_COLS - 1) / DELTA_COLS);
-    dim3 block(DELTA_COLS * DELTA_SLICES);
-    const size_t smem = (size_t)(DELTA_STAGE * 3 * dim + DELTA_STAGE * DELTA_COLS + DELTA_STAGE) * sizeof(float);
-#define DELTA_LAUNCH(N) return acorn_launch(delta_rule_kernel<N>, grid, block, smem, stream, qn, kn, vv, beta, g, state, \
-                                            slot_stride, row_start, row_slot, out, H, KH, dim, vdim)
-    if (dim <= 32) DELTA_LAUNCH(8);
-    if (dim <= 64) DELTA_LAUNCH(16);
-    if (dim <= 128) DELTA_LAUNCH(32);
-    DELTA_LAUNCH(64);
+    if (H > 65535 || vdim > 65535 || dim > 256 || H % KH) return ACORN_ERR_UNSUPPORTED;
+    dim3 block(DELTA_THREADS);
+    const int stage = dim <= 128 ? 16 : 8;
+#define DELTA_LAUNCH(N, SL)                                                                                                   \
+    do {                                                                                                                      \
+        const int cols = DELTA_THREADS / (SL);                                                                                \
+        dim3 grid(rows, H, (vdim + cols - 1) / cols);                                                                         \
+        const size_t smem = ((size_t)stage * (N) * (SL) * 4 + (size_t)2 * stage * 3 * dim + 2 * stage * cols + 3 * stage) *    \
+                            sizeof(float);                                                                                    \
+        static AcornPerDevice configured;                                                                                     \
+        if (!configured.seen()) {                                                                                             \
+            cudaError_t e = cudaFuncSetAttribute(delta_rule_kernel<N, SL>, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
+                                                 100 * 1024);                                                                 \
+            if (e != cudaSuccess) return (int)e;                                                                              \
+            configured.mark();                                                                                                \
+        }                                                                                                                     \
+        return acorn_launch(delta_rule_kernel<N, SL>, grid, block, smem, stream, qn, kn, vv, beta, g, state, slot_stride,     \
+                            row_start, row_slot, out, H, KH, dim, vdim, stage);                                               \
+    } while (0)
+    if (dim <= 32) DELTA_LAUNCH(8, 4);
+    if (dim <= 64) DELTA_LAUNCH(16, 4);
+    if (dim <= 128) DELTA_LAUNCH(16, 8);
+    DELTA_LAUNCH(32, 8);
 #undef DELTA_LAUNCH
 }
 

@@ -214,6 +214,7 @@ _TINY_DELTA = ChannelDeltaConfig(heads=1, kv_heads=1, dim=4, vdim=4, conv=1, dec
 SOLOS = {
     "delta rule, grouped heads, 4 taps": _solo(ChannelDeltaConfig(heads=6, kv_heads=2, dim=10, vdim=28, conv=4, decay_rank=3, gate_rank=5)),
     "delta rule, heads of 72 key channels": _solo(ChannelDeltaConfig(heads=1, kv_heads=1, dim=72, vdim=8, conv=2, decay_rank=4, gate_rank=4)),
+    "delta rule, heads of 136 key channels": _solo(ChannelDeltaConfig(heads=2, kv_heads=1, dim=136, vdim=20, conv=3, decay_rank=4, gate_rank=4)),
     "latent attention, window 5, scaled positions": _solo(LatentAttentionConfig(
         heads=3, dim=8, rot_dim=6, vdim=10, kv_rank=12, scale=0.4, rot_dims=6, rot_base=100.0,
         scaling=RotaryScaling(3.0, 8, 2.0, 0.5), window=5)),
