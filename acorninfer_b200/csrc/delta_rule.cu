@@ -235,18 +235,19 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(
         __syncthreads();
         const float* v_s = sv + (s & 1) * stage * DELTA_COLS;
         const float* b_s = sb + (s & 1) * stage;
-        constexpr int UNROLL = DPT <= 16 ? 2 : 1;                      // (more would spill the state)
-#pragma unroll UNROLL
+#pragma unroll 2
         for (int tt = 0; tt < n; ++tt) {
-            const float4* p = pack + tt * DIMP + slice;                // this thread's channels: every fourth entry
+            const float4* p = pack + tt * DIMP + slice;                // this thread's channels: every SLICES-th entry
+            float4 e[DPT];
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) e[i] = p[DELTA_SLICES * i];
             float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
 #pragma unroll
             for (int i = 0; i < DPT; i += 2) {
-                const float4 e0 = p[DELTA_SLICES * i], e1 = p[DELTA_SLICES * (i + 1)];
-                a0 = fmaf(S[i], e0.x, a0);
-                b0 = fmaf(S[i], e0.y, b0);
-                a1 = fmaf(S[i + 1], e1.x, a1);
-                b1 = fmaf(S[i + 1], e1.y, b1);
+                a0 = fmaf(S[i], e[i].x, a0);
+                b0 = fmaf(S[i], e[i].y, b0);
+                a1 = fmaf(S[i + 1], e[i + 1].x, a1);
+                b1 = fmaf(S[i + 1], e[i + 1].y, b1);
             }
             float a = a0 + a1, b = b0 + b1;
 #pragma unroll
@@ -257,10 +258,7 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(
             const float u = b_s[tt] * (v_s[tt * DELTA_COLS + col] - a);
             if (slice == 0 && live) out[((int64_t)(t0 + tt) * H + h) * vdim + column] = fmaf(skq[tt], u, b);
 #pragma unroll
-            for (int i = 0; i < DPT; ++i) {
-                const float4 e = p[DELTA_SLICES * i];
-                S[i] = fmaf(e.w, u, e.z * S[i]);
-            }
+            for (int i = 0; i < DPT; ++i) S[i] = fmaf(e[i].w, u, e[i].z * S[i]);
         }
         __syncthreads();                                               // pack and this stage's rows are free again
     }
@@ -295,10 +293,14 @@ extern "C" int acorn_delta_rule(const float* qn, const float* kn, const float* v
         return acorn_launch(delta_rule_kernel<N, SL>, grid, block, smem, stream, qn, kn, vv, beta, g, state, slot_stride,     \
                             row_start, row_slot, out, H, KH, dim, vdim, stage);                                               \
     } while (0)
-    if (dim <= 32) DELTA_LAUNCH(8, 4);
-    if (dim <= 64) DELTA_LAUNCH(16, 4);
-    if (dim <= 128) DELTA_LAUNCH(16, 8);
-    DELTA_LAUNCH(32, 8);
+    // a thread holds few state entries (4; 8 for the widest heads): a warp is alone on its scheduler, so the
+    // time of a token is the number of instructions a thread issues for it, and spreading a column over more
+    // lanes (up to a whole warp) shortens it although the reduction grows
+    if (dim <= 16) DELTA_LAUNCH(4, 4);
+    if (dim <= 32) DELTA_LAUNCH(4, 8);
+    if (dim <= 64) DELTA_LAUNCH(4, 16);
+    if (dim <= 128) DELTA_LAUNCH(4, 32);
+    DELTA_LAUNCH(8, 32);
 #undef DELTA_LAUNCH
 }
 

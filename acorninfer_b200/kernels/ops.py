@@ -105,6 +105,9 @@ class _Sigs:
     acorn_latent_prep = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
                          c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                          c_int, c_void_p]
+    acorn_latent_attention_tc = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                 c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p]
+    acorn_latent_attention_tc_supported = [c_int, c_int, c_int, c_int]
     acorn_head_linear = [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int,
                          c_int, c_void_p]
     acorn_delta_prep = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p,
@@ -1056,6 +1059,35 @@ def latent_prep(proj: torch.Tensor, qcat: torch.Tensor, c_weight32: torch.Tensor
                                 rot_dims, P, float(eps), 1 if write else 0, dtype_code(proj.dtype), _stream()), "latent_prep")
 
 
+LATENT_TILE_ROWS = 64          # (token, head) pairs a block of the tensor-core kernel takes
+
+
+def latent_attention_tc_supported(dtype: torch.dtype, num_heads: int, head_dim: int, value_dim: int, page_size: int) -> bool:
+    return dtype == torch.bfloat16 and bool(lib().acorn_latent_attention_tc_supported(num_heads, head_dim, value_dim, page_size))
+
+
+def latent_attention_tc(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor, page_base: torch.Tensor,
+                        row_start: torch.Tensor, row_pos: torch.Tensor, tiles: torch.Tensor, sink32: torch.Tensor | None,
+                        scale: float, window: int | None, value_dim: int) -> torch.Tensor:
+    """Attention of q [T, H, d] (bfloat16) over one cached row of d per token (pages [pages, 1, P, d]) whose
+    first ``value_dim`` entries are the values: returns [T, H, value_dim].  ``tiles`` int32 [n, 2]: (row, first
+    token within the row) of every group of ``LATENT_TILE_ROWS // H`` tokens."""
+    _check(q, "q", torch.bfloat16, 3)
+    _check(pages, "pages", torch.bfloat16, 4)
+    _check(tiles, "tiles", torch.int32, 2)
+    T, H, d = q.shape
+    if pages.shape[1] != 1 or pages.shape[3] != d:
+        raise KernelError(f"latent_attention_tc: pages {tuple(pages.shape)} do not fit one row of {d} per token")
+    if sink32 is not None:
+        _check(sink32, "sink", torch.float32, 1)
+    out = torch.empty((T, H, value_dim), dtype=torch.bfloat16, device=q.device)
+    _ok(lib().acorn_latent_attention_tc(q.data_ptr(), out.data_ptr(), pages.data_ptr(), block_table.data_ptr(),
+                                        page_base.data_ptr(), block_table.stride(0), row_start.data_ptr(), row_pos.data_ptr(),
+                                        tiles.data_ptr(), tiles.shape[0], _ptr(sink32), float(scale), int(window or 0), H, d,
+                                        int(value_dim), pages.shape[2], _stream()), "latent_attention_tc")
+    return out
+
+
 def head_linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
     """y[t, h, :] = w[h] x[t, h, :] for every head.  x [T, H, I] and y [T, H, O] may be views with any
     token and head strides (innermost contiguous); w [H, O, I] contiguous."""
@@ -1065,6 +1097,14 @@ def head_linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> torch.Tens
         raise KernelError(f"head_linear: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)} do not fit")
     if x.stride(2) != 1 or y.stride(2) != 1 or not x.is_cuda or not y.is_cuda:
         raise KernelError("head_linear: innermost dimensions must be contiguous CUDA memory")
+    if x.dtype == torch.bfloat16 and x.shape[0] > GEMM_TC_MAX_ROWS:
+        # many rows: the library's batched product (one batch entry a head), as the plain products of such steps
+        if _TIMER is not None:
+            _TIMER.begin()
+        torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out=y.transpose(0, 1))
+        if _TIMER is not None:
+            _TIMER.end("library_bmm", f"{x.shape[0]}x{H}x{O}x{I}")
+        return y
     _ok(lib().acorn_head_linear(x.data_ptr(), x.stride(0), x.stride(1), w.data_ptr(), y.data_ptr(), y.stride(0), y.stride(1),
                                 x.shape[0], H, O, I, dtype_code(x.dtype), _stream()), "head_linear", f"{x.shape[0]}x{H}x{O}x{I}")
     return y

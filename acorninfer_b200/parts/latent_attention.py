@@ -70,6 +70,20 @@ class LatentAttention(Mixer):
     def cache_needs(self):
         return CacheNeeds(kv=KVNeeds(1, self.rank + self.rot, self.window, values=False))
 
+    def _tile_tokens(self):
+        return max(1, ops.LATENT_TILE_ROWS // self.H)
+
+    def step_arrays(self):
+        # the tensor-core kernel's tiles: (row, first token within the row) of every group of 64 // H tokens
+        import numpy as np
+        n = self._tile_tokens()
+
+        def tiles(plan):
+            t = [(r, q0) for r, length in enumerate(plan.row_lens) for q0 in range(0, length, n)]
+            return np.asarray(t, np.int32).reshape(-1, 2)
+
+        return {f"latent.tiles{n}": tiles}
+
     def forward(self, x, inputs, cache):
         if cache.write != self.own_cache:
             raise ValueError("latent attention: the schedule and the layer disagree on who writes the cache")
@@ -83,10 +97,15 @@ class LatentAttention(Mixer):
                         g.page_base, cache.k_pages if cache.write else None, H, self.dim, self.rot, self.rank,
                         pos.rotary_dim if pos is not None else 0, self.eps)
         qu = proj[:, :H * (self.dim + self.rot)].view(T, H, self.dim + self.rot)[:, :, :self.dim]
-        ops.head_linear(qu, self.w_uk_t.to(dt) if self.w_uk_t.dtype != dt else self.w_uk_t, qcat[:, :, :self.rank])
-        o = ops.attention_plain(qcat, qcat.stride(0), cache.k_pages, cache.k_pages, g.block_table, g.page_base,
-                                inputs.token_row, inputs.positions, T, H, 1, self.rank + self.rot, self.scale,
-                                self.window, value_dim=self.rank, sink32=self.sink32)
+        ops.head_linear(qu, self.w_uk_t, qcat[:, :, :self.rank])
+        if ops.latent_attention_tc_supported(dt, H, self.rank + self.rot, self.rank, cache.k_pages.shape[2]):
+            o = ops.latent_attention_tc(qcat, cache.k_pages, g.block_table, g.page_base, inputs.row_start, inputs.row_pos,
+                                        inputs.extra[f"latent.tiles{self._tile_tokens()}"], self.sink32, self.scale,
+                                        self.window, self.rank)
+        else:       # float32, or sizes the tensor-core kernel does not take
+            o = ops.attention_plain(qcat, qcat.stride(0), cache.k_pages, cache.k_pages, g.block_table, g.page_base,
+                                    inputs.token_row, inputs.positions, T, H, 1, self.rank + self.rot, self.scale,
+                                    self.window, value_dim=self.rank, sink32=self.sink32)
         v = torch.empty((T, H, self.vdim), dtype=dt, device=x.device)
         ops.head_linear(o.view(T, H, self.rank), self.w_uv, v)
         return ops.linear(v.view(T, H * self.vdim), self.w_o, out_dtype=dt)

@@ -281,7 +281,7 @@ def test_grouped_products_take_each_experts_own_rows():
                 assert (out[s] - x[t] @ w[e].T).abs().max() < 1e-4
 
 
-def _latent_case(befores, qlens, P, d, dv, nq, window, spikes, dtype, sink_value=None, seed=0):
+def _latent_case(befores, qlens, P, d, dv, nq, window, spikes, dtype, sink_value=None, seed=0, kernel="plain"):
     """Cache rows and queries for ``attention_plain`` in the latent layout (one kv head, values = the
     first dv entries of the key rows).  ``spikes``: (row, key position): that key and all queries of the
     row get a large component along one direction, so its score stands out wherever it is seen."""
@@ -306,9 +306,19 @@ def _latent_case(befores, qlens, P, d, dv, nq, window, spikes, dtype, sink_value
     q_new = torch.cat([fq[b:] for fq, b in zip(full_q, befores)]).to(dtype).to(DEV).contiguous()
     sink = None if sink_value is None else torch.full((nq,), float(sink_value)) + torch.arange(nq) * 0.5
     scale = 0.5
-    out = ops().attention_plain(q_new.view(-1, nq * d), nq * d, pages, pages, lay["block_table"], lay["page_base"],
-                                lay["token_row"], lay["positions"], lay["num_tokens"], nq, 1, d, scale, window,
-                                value_dim=dv, sink32=None if sink is None else sink.to(DEV)).float().cpu()
+    if kernel == "tc":
+        o = ops()
+        assert o.latent_attention_tc_supported(dtype, nq, d, dv, P)
+        n = o.LATENT_TILE_ROWS // nq
+        i32 = dict(dtype=torch.int32, device=DEV)
+        tiles = torch.tensor([(r, q0) for r, length in enumerate(qlens) for q0 in range(0, length, n)], **i32)
+        out = o.latent_attention_tc(q_new, pages, lay["block_table"], lay["page_base"],
+                                    torch.tensor(np.cumsum([0] + qlens), **i32), torch.tensor(befores, **i32), tiles,
+                                    None if sink is None else sink.to(DEV), scale, window, dv).float().cpu()
+    else:
+        out = ops().attention_plain(q_new.view(-1, nq * d), nq * d, pages, pages, lay["block_table"], lay["page_base"],
+                                    lay["token_row"], lay["positions"], lay["num_tokens"], nq, 1, d, scale, window,
+                                    value_dim=dv, sink32=None if sink is None else sink.to(DEV)).float().cpu()
     want = []
     for fq, fk, b in zip(full_q, full_k, befores):
         heads = []
@@ -320,28 +330,30 @@ def _latent_case(befores, qlens, P, d, dv, nq, window, spikes, dtype, sink_value
     return out.view(-1, nq, dv), torch.cat(want)
 
 
-@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2e-2)])
-def test_latent_layout_attention_window_edges_far_keys_and_sink(dtype, tol):
+@pytest.mark.parametrize("dtype,tol,kernel,d,dv,nq", [(torch.float32, 2e-5, "plain", 24, 16, 3), (torch.bfloat16, 2e-2, "plain", 24, 16, 3),
+                                                      (torch.bfloat16, 2e-2, "tc", 32, 16, 3), (torch.bfloat16, 2e-2, "tc", 112, 96, 8),
+                                                      (torch.bfloat16, 2e-2, "tc", 160, 144, 16)])
+def test_latent_layout_attention_window_edges_far_keys_and_sink(dtype, tol, kernel, d, dv, nq):
     """A key that outweighs all others is seen up to the query window - 1 tokens after it and no
     longer, in a prompt's rows and in single decoded tokens, at page borders; a far key among hundreds
     is found without a window; a sink takes its share of every row."""
-    P, d, dv, nq, W = 16, 24, 16, 3, 64
+    P, W = 16, 64
     # row 0: a whole prompt; row 1: a portion after 130 cached tokens; rows 2-5: single tokens whose
     # window's first key (2, 4) or the key just before it (3, 5) is the spiked one, at a page's border or not
     befores = [0, 130, 15 + W - 1, 15 + W, 16 + W - 1, 16 + W]
     qlens = [300, 90, 1, 1, 1, 1]
     spikes = [(0, 15), (0, 16), (0, 200), (1, 100), (1, 131), (2, 15), (3, 15), (4, 16), (5, 16)]
-    got, want = _latent_case(befores, qlens, P, d, dv, nq, W, spikes, dtype, sink_value=0.5)
+    got, want = _latent_case(befores, qlens, P, d, dv, nq, W, spikes, dtype, sink_value=0.5, kernel=kernel)
     assert (got - want).abs().max() < tol
     # the spiked key decides the rows that see it: the decoded token of row 2 returns (nearly) its
     # value, the one of row 3, one position later, does not
     lay_tokens = np.cumsum([0] + qlens)
     assert (got[lay_tokens[2]] - got[lay_tokens[3]]).abs().max() > 0.05
     # no window: key 3 of 700 decides a decoded token's result
-    got, want = _latent_case([0, 699], [40, 1], P, d, dv, nq, None, [(1, 3)], dtype)
+    got, want = _latent_case([0, 699], [40, 1], P, d, dv, nq, None, [(1, 3)], dtype, kernel=kernel)
     assert (got - want).abs().max() < tol
     # a sink that outweighs the keys leaves almost nothing
-    got, want = _latent_case([5], [20], P, d, dv, nq, 8, [], dtype, sink_value=12.0)
+    got, want = _latent_case([5], [20], P, d, dv, nq, 8, [], dtype, sink_value=12.0, kernel=kernel)
     assert (got - want).abs().max() < tol and got.abs().max() < 0.05
 
 
