@@ -151,7 +151,7 @@ extern "C" int acorn_conv_state_update(const void* main_, int64_t ld, float* sta
 // token overlaps the sums of the next.  The tokens' q, k, g, v, beta come through shared memory, `stage`
 // tokens at a time: the next stage's rows are fetched (cp.async) while this one is computed; gk, gq, g, k
 // are packed per channel into one 16-byte entry, and k . q is summed, once per stage.
-#define DELTA_THREADS 128
+#define DELTA_THREADS 256
 
 __device__ __forceinline__ void cp_async_4(float* dst, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src));
@@ -296,10 +296,11 @@ extern "C" int acorn_delta_rule(const float* qn, const float* kn, const float* v
     // a thread holds few state entries (4; 8 for the widest heads): a warp is alone on its scheduler, so the
     // time of a token is the number of instructions a thread issues for it, and spreading a column over more
     // lanes (up to a whole warp) shortens it although the reduction grows
+    // (the tokens' staging is shared by a block's columns: 256 threads keep 8 to 64 columns together)
     if (dim <= 16) DELTA_LAUNCH(4, 4);
     if (dim <= 32) DELTA_LAUNCH(4, 8);
     if (dim <= 64) DELTA_LAUNCH(4, 16);
-    if (dim <= 128) DELTA_LAUNCH(4, 32);
+    if (dim <= 128) DELTA_LAUNCH(8, 16);
     DELTA_LAUNCH(8, 32);
 #undef DELTA_LAUNCH
 }
