@@ -682,7 +682,8 @@ def design_bench(args) -> int:
 
             def decode_entries():
                 reqs = synthetic_requests(runner, 8, context - 8, "kt_d")
-                return [StepEntry(rc, [5], [0]) for rc in reqs], (lambda: [runner.close(rc) for rc in reqs])
+                return ([StepEntry(rc, [(5 + 7919 * i) % runner.vocab_size], [0]) for i, rc in enumerate(reqs)],
+                        (lambda: [runner.close(rc) for rc in reqs]))
 
             r["kernels_prefill_2048"] = kernel_times(runner, prefill_entries, torch)
             r["kernels_decode_b8"] = kernel_times(runner, decode_entries, torch)
