@@ -1,11 +1,11 @@
 """A routed mixture of small SwiGLU experts, some of which are the identity, as a feed-forward.
 
 Router logits ``z = W_router h`` over ``experts + identity`` outputs, in float32; scores
-``s = softmax(z)``; the choice scores are ``s + correction``.  The outputs form ``groups`` equal groups
-of neighbours, a group's score is its largest choice score, and only outputs of the ``keep`` best groups
-can be chosen (the others count as minus infinity).  The ``top`` largest choice scores win; their
-weights are ``s`` itself, not renormalized.  The last ``identity`` outputs are identity experts: no
-tensors, output = input.  A real expert is ``down(silu(gate h) * (up h))``.  The result is the weighted
+``s = softmax(z)``; experts are ranked by ``s + correction``.  Neighbouring outputs form ``groups`` groups of
+equal size; a group is ranked by the best ranking value inside it, and outputs outside the ``keep`` best
+groups are out of the running whatever their value.  The ``top`` best-ranked outputs are taken, each
+weighted by its own ``s`` (the correction only ranks; the weights are left as they are, not rescaled to
+sum to one).  The last ``identity`` outputs own no tensors and pass their input through.  A real expert is ``down(silu(gate h) * (up h))``.  The result is the weighted
 sum over the chosen.
 
 On the device: the router's choice (one kernel), the (token, choice) pairs grouped by expert (one

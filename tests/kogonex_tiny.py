@@ -50,7 +50,7 @@ KOGO_C = dict(page_size=16, seed=33, cfg=KogonexConfig(
     vocab_size=320, hidden_size=128, norm_eps=1e-5, bigram_buckets=211, bigram_mul_prev=5, bigram_mul_cur=3, layers=(
         KogonexLayer(ChannelDeltaConfig(heads=2, kv_heads=1, dim=64, vdim=64, conv=3, decay_rank=8, gate_rank=16),
                      RoutedExpertsConfig(ff=64, experts=8, identity=0, top=2, groups=2, keep=1)),
-        KogonexLayer(LatentAttentionConfig(heads=4, dim=32, rot_dim=16, vdim=32, kv_rank=64, scale=0.15, rot_dims=16,
+        KogonexLayer(LatentAttentionConfig(heads=4, dim=48, rot_dim=16, vdim=40, kv_rank=64, scale=0.15, rot_dims=16,
                                            rot_base=1e6, scaling=RotaryScaling(4.0, 64, 16.0, 1.0), window=40),
                      RoutedExpertsConfig(ff=64, experts=6, identity=2, top=3, groups=2, keep=2)),
         KogonexLayer(LatentAttentionConfig(heads=2, dim=64, rot_dim=16, vdim=48, kv_rank=64, scale=0.1, rot_dims=16,

@@ -74,7 +74,7 @@ def test_model_as_data_and_cache_needs():
 
 
 def test_scaled_rotary_constants_match_plain():
-    for dims, base, sc in ((16, 1e6, dict(factor=4.0, original=2048, fast=32.0, slow=1.0)), (8, 1e4, dict(factor=8.0, original=16, fast=4.0, slow=0.5)),
+    for dims, base, sc in ((16, 5e5, dict(factor=6.0, original=1024, fast=16.0, slow=2.0)), (8, 1e4, dict(factor=8.0, original=16, fast=4.0, slow=0.5)),
                            (32, 5e5, dict(factor=2.5, original=100, fast=20.0, slow=3.0))):
         rope = ScaledRope(BuildContext(torch.float32, torch.device("cpu"), 16), dims, base, rotary_dim=dims, **sc)
         f, mag = plain.rotary_frequencies({"dims": dims, "base": base, "scaling": sc})
