@@ -240,8 +240,8 @@ __global__ void __launch_bounds__(256) grouped_gemm_kernel(const T* __restrict__
 
 // ---------------------------------------------------------------- the same on the tensor cores (bfloat16)
 // mma.sync m16n8k16, float32 accumulation in the order of K.  A block: BM slots of one expert by 128
-// weight rows; eight warps; operand tiles of 64 along K through a ring of cp.async stages.  BM = 64
-// (warps 2 x 4, 32 x 32 each) for steps with many rows an expert, BM = 16 (warps 1 x 8, 16 x 16 each) for
+// weight rows; eight warps; operand tiles of 64 along K through a ring of cp.async stages.  BM = 128 or 64
+// (warps 2 x 4, 64 x 32 or 32 x 32 each) for steps with many rows an expert, BM = 16 (warps 1 x 8, 16 x 16 each) for
 // decode steps, where the kernel is bound by reading every chosen expert's matrix once.  An output
 // element is the same chain of products in both, so a row's bits do not depend on the step it is in.
 #define GT_BN 128
@@ -289,7 +289,7 @@ __global__ void __launch_bounds__(256) grouped_gemm_tc_kernel(const bf16* __rest
     const int n0 = blockIdx.x * GT_BN;
     const bf16* We = W + (int64_t)e * N * K;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    constexpr int WM = BM == 64 ? 2 : 1;                 // warps along the slots
+    constexpr int WM = BM >= 64 ? 2 : 1;                 // warps along the slots
     constexpr int WN = 8 / WM;                           // warps along the weight rows
     constexpr int MT = BM / WM / 16;                     // 16-row tiles a warp
     constexpr int NT = GT_BN / WN / 8;                   // 8-column tiles a warp
@@ -394,6 +394,8 @@ extern "C" int acorn_grouped_gemm(const void* A, int64_t lda, const int* a_rows,
         // few rows an expert on average: the small tile (a decode step); else the large one
         if ((int64_t)slots <= (int64_t)16 * E)
             return grouped_gemm_tc_launch<16>((const bf16*)A, lda, a_rows, (const bf16*)W, (bf16*)C, ldc, offsets, slots, E, N, K, stream);
+        if ((int64_t)slots >= (int64_t)256 * E)          // several full tiles an expert: the tall tile (64 x 32 a warp)
+            return grouped_gemm_tc_launch<128>((const bf16*)A, lda, a_rows, (const bf16*)W, (bf16*)C, ldc, offsets, slots, E, N, K, stream);
         return grouped_gemm_tc_launch<64>((const bf16*)A, lda, a_rows, (const bf16*)W, (bf16*)C, ldc, offsets, slots, E, N, K, stream);
     }
     const int64_t tiles = (slots + GG_BM - 1) / GG_BM + E;       // every expert may end in a partly filled tile
