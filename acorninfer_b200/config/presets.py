@@ -1,6 +1,7 @@
 """Sizes of published Qwen3 dense models as ``config.json`` dictionaries, for runs with random
 weights (benchmarks, the random-weights mode): no checkpoint is needed to measure at a model's
-layer sizes.  Only the keys the architecture reads are given."""
+layer sizes.  Only the keys the architecture reads are given.  For Kogonex, of which no model is
+published, two size sets with layers as wide as real models have them."""
 
 from __future__ import annotations
 
@@ -22,8 +23,42 @@ PRESETS: dict[str, dict] = {
 }
 
 
+def _kogonex(width: int, vocab: int, heads: int, dim: int, rot: int, vdim: int, rank: int, window: int, d_heads: int,
+             d_kv_heads: int, d_dim: int, d_vdim: int, taps: int, decay_rank: int, gate_rank: int, ff: int, experts: int,
+             identity: int, top: int, groups: int, keep: int, repeats: int = 2) -> dict:
+    """Layers in the pattern delta, latent, delta, delta, latent-reading-the-other's-cache, ``repeats`` times."""
+    mlp = {"kind": "moe", "expert": {"ff": ff},
+           "router": {"experts": experts, "identity": identity, "top": top, "groups": {"count": groups, "keep": keep}}}
+    delta = {"heads": d_heads, "kv_heads": d_kv_heads, "dim": d_dim, "vdim": d_vdim, "conv": taps,
+             "decay_rank": decay_rank, "gate_rank": gate_rank}
+    latent = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "kv_rank": rank, "scale": (dim + rot) ** -0.5,
+              "mask": {"size": window},
+              "rot": {"base": 1e6, "dims": rot, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    layers = []
+    for _ in range(repeats):
+        for kind in ("delta", "latent", "delta", "delta", "shared"):
+            if kind == "delta":
+                layers.append({"type": "channel_delta", "mixer": dict(delta), "mlp": mlp})
+            else:
+                mixer = dict(latent, kv_from=len(layers) - 3) if kind == "shared" else dict(latent)
+                layers.append({"type": "latent_attention", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Kogonex", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "embedding": {"bigram": {"buckets": 100003, "mul_prev": 1000003, "mul_cur": 31}}, "layers": layers}
+
+
+PRESETS.update({
+    "kogonex-w1024": _kogonex(1024, 32768, heads=8, dim=64, rot=32, vdim=64, rank=192, window=512, d_heads=8, d_kv_heads=4,
+                              d_dim=64, d_vdim=128, taps=4, decay_rank=32, gate_rank=64, ff=512, experts=14, identity=2,
+                              top=4, groups=4, keep=2),
+    "kogonex-w2048": _kogonex(2048, 65536, heads=16, dim=128, rot=64, vdim=128, rank=384, window=1024, d_heads=16,
+                              d_kv_heads=8, d_dim=128, d_vdim=128, taps=4, decay_rank=64, gate_rank=128, ff=1024, experts=30,
+                              identity=2, top=6, groups=4, keep=2),
+})
+
+
 def preset(name: str) -> dict:
     try:
-        return dict(PRESETS[name.lower()])
+        import copy
+        return copy.deepcopy(PRESETS[name.lower()])
     except KeyError:
         raise ValueError(f"no preset {name!r}; there are {', '.join(sorted(PRESETS))}") from None

@@ -577,37 +577,13 @@ def reference_arm(args) -> int:
 
 # ------------------------------------------------------------------ Kogonex beside Qwen3 at equal size
 
-KOGONEX_SIZES = {
-    # width, vocabulary, layers as (mixer kind, ...) patterns; all sizes of a layer as a real model has them
-    "w1024": dict(width=1024, vocab=32768, heads=8, dim=64, rot=32, vdim=64, rank=192, window=512,
-                  d_heads=8, d_kv_heads=4, d_dim=64, d_vdim=128, taps=4, decay_rank=32, gate_rank=64,
-                  ff=512, experts=14, identity=2, top=4, groups=4, keep=2),
-    "w2048": dict(width=2048, vocab=65536, heads=16, dim=128, rot=64, vdim=128, rank=384, window=1024,
-                  d_heads=16, d_kv_heads=8, d_dim=128, d_vdim=128, taps=4, decay_rank=64, gate_rank=128,
-                  ff=1024, experts=30, identity=2, top=6, groups=4, keep=2),
-}
-KOGONEX_PATTERN = ("delta", "latent", "delta", "delta", "shared")       # five layers, repeated
+KOGONEX_SIZES = ("w1024", "w2048")        # presets "kogonex-<name>" of acorninfer_b200/config/presets.py
 
 
-def kogonex_config(z: dict, repeats: int):
-    from acorninfer_b200.config.model_config import (ChannelDeltaConfig, KogonexConfig, KogonexLayer, LatentAttentionConfig,
-                                                     RotaryScaling, RoutedExpertsConfig)
-    layers = []
-    moe = RoutedExpertsConfig(ff=z["ff"], experts=z["experts"], identity=z["identity"], top=z["top"], groups=z["groups"],
-                              keep=z["keep"])
-    for r in range(repeats):
-        for kind in KOGONEX_PATTERN:
-            if kind == "delta":
-                m = ChannelDeltaConfig(heads=z["d_heads"], kv_heads=z["d_kv_heads"], dim=z["d_dim"], vdim=z["d_vdim"],
-                                       conv=z["taps"], decay_rank=z["decay_rank"], gate_rank=z["gate_rank"])
-            else:
-                m = LatentAttentionConfig(heads=z["heads"], dim=z["dim"], rot_dim=z["rot"], vdim=z["vdim"], kv_rank=z["rank"],
-                                          scale=(z["dim"] + z["rot"]) ** -0.5, rot_dims=z["rot"], rot_base=1e6,
-                                          scaling=RotaryScaling(4.0, 4096, 32.0, 1.0), window=z["window"],
-                                          kv_from=(len(layers) - 3) if kind == "shared" else None)
-            layers.append(KogonexLayer(m, moe))
-    return KogonexConfig(vocab_size=z["vocab"], hidden_size=z["width"], norm_eps=1e-5, layers=tuple(layers),
-                         bigram_buckets=100003, bigram_mul_prev=1000003, bigram_mul_cur=31)
+def kogonex_config(name: str):
+    from acorninfer_b200.config.presets import preset
+    from acorninfer_b200.registry import config_from_dict
+    return config_from_dict(preset(f"kogonex-{name}"))
 
 
 def kernel_times(runner, entries_fn, torch) -> dict:
@@ -650,14 +626,15 @@ def design_bench(args) -> int:
            "warmup": args.warmup, "peaks": pk, "sizes": {}}
     context, prompt = 2048, 2048
     for name in (args.design_sizes.split(",") if args.design_sizes else list(KOGONEX_SIZES)):
-        z = KOGONEX_SIZES[name]
-        repeats = 2
+        kcfg = kogonex_config(name)
+        latent = next(l.mixer for l in kcfg.layers if hasattr(l.mixer, "kv_rank"))
+        moe = kcfg.layers[0].mlp
         models = {
-            "kogonex": kogonex_config(z, repeats),
-            "qwen3": Qwen3Config(num_hidden_layers=repeats * len(KOGONEX_PATTERN), hidden_size=z["width"],
-                                 num_attention_heads=z["heads"], num_key_value_heads=max(1, z["heads"] // 4), head_dim=128,
-                                 intermediate_size=z["top"] * z["ff"], rms_norm_eps=1e-6, rope_theta=1e6,
-                                 vocab_size=z["vocab"], tie_word_embeddings=False, bos_token_id=None, eos_token_id=()),
+            "kogonex": kcfg,
+            "qwen3": Qwen3Config(num_hidden_layers=len(kcfg.layers), hidden_size=kcfg.hidden_size,
+                                 num_attention_heads=latent.heads, num_key_value_heads=max(1, latent.heads // 4), head_dim=128,
+                                 intermediate_size=moe.top * moe.ff, rms_norm_eps=1e-6, rope_theta=1e6,
+                                 vocab_size=kcfg.vocab_size, tie_word_embeddings=False, bos_token_id=None, eos_token_id=()),
         }
         res = {}
         for which, cfg in models.items():
