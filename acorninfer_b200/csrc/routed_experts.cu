@@ -406,14 +406,19 @@ extern "C" int acorn_grouped_gemm(const void* A, int64_t lda, const int* a_rows,
     return ACORN_ERR_UNSUPPORTED;
 }
 
-// out[t, :] = sum over the token's choices, in their order
+// out[t, :] = sum over the token's choices, in their order.  With resid32: the float32 sums of the row are
+// RMS-normed (x / sqrt(mean(x^2) + eps) * w) and added to resid32[t], and `out` (if given) receives the new
+// stream rounded to T: the feed-forward's output norm and residual sum without a kernel of their own.
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ y, const T* __restrict__ x, const int* __restrict__ slot_of,
                                    const int* __restrict__ idx, const float* __restrict__ wts, T* __restrict__ out, int H,
-                                   int top, int E) {
+                                   int top, int E, float* __restrict__ resid32, const float* __restrict__ norm_w, float eps) {
+    extern __shared__ float row_s[];                    // [H] the row's sums (fused form only)
+    __shared__ float scratch[32];
     pdl_wait();
     pdl_trigger();
     const int64_t t = blockIdx.x;
+    float ss = 0.f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float acc = 0.f;
         for (int k = 0; k < top; ++k) {
@@ -421,14 +426,30 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const T* __restrict_
             const float v = idx[p] >= E ? to_float(x[t * H + i]) : to_float(y[(int64_t)slot_of[p] * H + i]);
             acc = fmaf(wts[p], v, acc);
         }
-        out[t * H + i] = from_float<T>(acc);
+        if (resid32) {
+            row_s[i] = acc;
+            ss += acc * acc;
+        } else {
+            out[t * H + i] = from_float<T>(acc);
+        }
+    }
+    if (!resid32) return;
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = resid32[t * H + i] + row_s[i] * inv * norm_w[i];
+        resid32[t * H + i] = v;
+        if (out) out[t * H + i] = from_float<T>(v);
     }
 }
 
 extern "C" int acorn_moe_combine(const void* y, const void* x, const int* slot_of, const int* idx, const float* wts, void* out,
-                                 int tokens, int H, int top, int E, int dtype, cudaStream_t stream) {
+                                 int tokens, int H, int top, int E, int dtype, float* resid32, const float* norm_w, float eps,
+                                 cudaStream_t stream) {
     if (tokens <= 0) return 0;
-    ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(moe_combine_kernel<T>, dim3(tokens), dim3(256), 0, stream, (const T*)y,
-                                                       (const T*)x, slot_of, idx, wts, (T*)out, H, top, E));
+    const size_t smem = resid32 ? (size_t)H * sizeof(float) : 0;
+    if (smem > 48 * 1024) return ACORN_ERR_UNSUPPORTED;
+    ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(moe_combine_kernel<T>, dim3(tokens), dim3(256), smem, stream, (const T*)y,
+                                                       (const T*)x, slot_of, idx, wts, (T*)out, H, top, E, resid32, norm_w, eps));
     return ACORN_ERR_UNSUPPORTED;
 }

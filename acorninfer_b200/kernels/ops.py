@@ -123,7 +123,7 @@ class _Sigs:
     acorn_grouped_gemm = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_int,
                           c_int, c_int, c_void_p]
     acorn_moe_combine = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                         c_void_p]
+                         c_void_p, c_void_p, c_float, c_void_p]
     acorn_attention_decode = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                               c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                               c_int, c_void_p, c_void_p, c_void_p]
@@ -1226,14 +1226,24 @@ def grouped_gemm(a: torch.Tensor, a_rows: torch.Tensor | None, w: torch.Tensor, 
 
 
 def moe_combine(y: torch.Tensor, x: torch.Tensor, slot_of: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor,
-                num_experts: int) -> torch.Tensor:
-    """out[t] = sum_k wts[t, k] * (idx[t, k] >= num_experts ? x[t] : y[slot_of[t, k]])."""
+                num_experts: int, resid32: torch.Tensor | None = None, weight32: torch.Tensor | None = None,
+                eps: float = 0.0) -> torch.Tensor | None:
+    """out[t] = sum_k wts[t, k] * (idx[t, k] >= num_experts ? x[t] : y[slot_of[t, k]]).  With ``resid32`` the
+    float32 sum is not returned but RMS-normed (``weight32``, ``eps``) and added to ``resid32`` in place; what
+    is returned is then the new stream rounded to ``x``'s dtype (None if that is float32)."""
     _check(y, "y", x.dtype, 2)
     _check(x, "x", None, 2)
     T, H = x.shape
-    out = torch.empty_like(x)
-    _ok(lib().acorn_moe_combine(y.data_ptr(), x.data_ptr(), slot_of.data_ptr(), idx.data_ptr(), wts.data_ptr(), out.data_ptr(),
-                                T, H, idx.shape[1], int(num_experts), dtype_code(x.dtype), _stream()), "moe_combine")
+    fused = resid32 is not None
+    if fused:
+        _check(resid32, "resid32", torch.float32, 2)
+        _check(weight32, "norm weight", torch.float32, 1)
+        if resid32.shape != x.shape or weight32.numel() != H:
+            raise KernelError("moe_combine: residual or norm weight do not fit")
+    out = None if (fused and x.dtype == torch.float32) else torch.empty_like(x)
+    _ok(lib().acorn_moe_combine(y.data_ptr(), x.data_ptr(), slot_of.data_ptr(), idx.data_ptr(), wts.data_ptr(), _ptr(out),
+                                T, H, idx.shape[1], int(num_experts), dtype_code(x.dtype), _ptr(resid32), _ptr(weight32),
+                                float(eps), _stream()), "moe_combine")
     return out
 
 # ------------------------------------------------------------------ sampling

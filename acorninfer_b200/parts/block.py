@@ -88,5 +88,10 @@ class OutputNormBlock(Block):
             h = self._rows(resid32, None)
         h = self._rows(resid32, self.norms["mixer"].normed_add(resid32, self.mixer.forward(h, inputs, cache)))
         if self.feed_forward is not None:
-            h = self._rows(resid32, self.norms["feed_forward"].normed_add(resid32, self.feed_forward.forward(h, inputs)))
+            norm = self.norms["feed_forward"]
+            if getattr(self.feed_forward, "adds_normed_residual", False) and hasattr(norm, "weight32"):
+                # the feed-forward's last kernel norms its result and adds it to the stream itself
+                h = self._rows(resid32, self.feed_forward.forward(h, inputs, add_normed=(resid32, norm)))
+            else:
+                h = self._rows(resid32, norm.normed_add(resid32, self.feed_forward.forward(h, inputs)))
         return resid32, ops.RoundedRows(h)

@@ -34,7 +34,7 @@ class RoutedExperts(FeedForward):
         self.ctx = ctx
         self.hidden_size, self.ff = hidden_size, expert_size
         self.E, self.I, self.top, self.groups, self.keep = num_experts, num_identity, top, groups, keep
-        self.w_router32 = self.correction32 = self.w_gate_up = self.w_down = None
+        self.w_router = self.correction32 = self.w_gate_up = self.w_down = None
 
     def tensor_specs(self):
         n = self.E + self.I
@@ -47,7 +47,10 @@ class RoutedExperts(FeedForward):
 
     def bind(self, tensors):
         t = tensors
-        self.w_router32 = t["router"].to(torch.float32).contiguous()
+        # Under a bfloat16 engine the router's matrix stays as stored: a product of two bfloat16 numbers is
+        # exact in float32, so the tensor-core product with float32 accumulation is the float32 computation
+        # on the rounded input, up to the order of the sum.
+        self.w_router = t["router"].contiguous()
         self.correction32 = t["correction"].to(torch.float32).contiguous()
         if self.E:
             mats = [t[f"e{e}.{n}"] for e in range(self.E) for n in ("gate", "up", "down")]
@@ -56,9 +59,11 @@ class RoutedExperts(FeedForward):
                                           for e in range(self.E)]).contiguous()               # [E, 2 ff, width]
             self.w_down = torch.stack([t[f"e{e}.down"].to(dtype) for e in range(self.E)]).contiguous()   # [E, width, ff]
 
-    def forward(self, x, inputs):
+    adds_normed_residual = True     # ``forward(..., add_normed=(resid32, norm))`` adds the normed result to the stream itself
+
+    def forward(self, x, inputs, add_normed=None):
         T = x.shape[0]
-        z = ops.linear(x, self.w_router32, out_dtype=torch.float32)
+        z = ops.linear(x, self.w_router, out_dtype=torch.float32)
         idx, wts = ops.moe_route(z, self.correction32, self.top, self.groups, self.keep)
         offsets, slot_of, slot_token = ops.moe_plan(idx, self.E + self.I)
         slots = T * self.top
@@ -69,4 +74,7 @@ class RoutedExperts(FeedForward):
             y = ops.grouped_gemm(hidden, None, w_dn, offsets, slots)
         else:
             y = x
+        if add_normed is not None:
+            resid32, norm = add_normed
+            return ops.moe_combine(y, x, slot_of, idx, wts, self.E, resid32=resid32, weight32=norm.weight32, eps=norm.eps)
         return ops.moe_combine(y, x, slot_of, idx, wts, self.E)

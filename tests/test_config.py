@@ -91,7 +91,10 @@ def test_presets_of_the_family_are_valid_configurations():
     from acorninfer_b200.registry import config_from_dict, spec_for
     for name, raw in PRESETS.items():
         cfg = config_from_dict(raw)
-        assert cfg.head_dim == 128 and cfg.num_attention_heads % cfg.num_key_value_heads == 0
+        if name.startswith("qwen3"):
+            assert cfg.head_dim == 128 and cfg.num_attention_heads % cfg.num_key_value_heads == 0
+        else:
+            assert name.startswith("kogonex") and len(cfg.layers) == 10 and cfg.layers[4].mixer.kv_from == 1
         spec_for(cfg)                                    # builds the model description
     assert preset("Qwen3-8B")["hidden_size"] == 4096
     import pytest
