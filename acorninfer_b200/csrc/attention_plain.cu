@@ -23,7 +23,7 @@
 #define PLAIN_LANES 128                 // threads across the dimensions of a head
 #define PLAIN_KGROUPS (PLAIN_THREADS / PLAIN_LANES)
 #define PLAIN_WARPS (PLAIN_THREADS / 32)
-#define PLAIN_MAX_D 512
+#define PLAIN_MAX_D 1024
 #define PLAIN_HEADS 8                   // query heads a block takes
 
 template <typename T>

@@ -235,7 +235,7 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(
         __syncthreads();
         const float* v_s = sv + (s & 1) * stage * DELTA_COLS;
         const float* b_s = sb + (s & 1) * stage;
-#pragma unroll 2
+#pragma unroll 4
         for (int tt = 0; tt < n; ++tt) {
             const float4* p = pack + tt * DIMP + slice;                // this thread's channels: every SLICES-th entry
             float4 e[DPT];
@@ -276,7 +276,7 @@ extern "C" int acorn_delta_rule(const float* qn, const float* kn, const float* v
     if (rows <= 0) return 0;
     if (H > 65535 || vdim > 65535 || dim > 256 || H % KH) return ACORN_ERR_UNSUPPORTED;
     dim3 block(DELTA_THREADS);
-    const int stage = dim <= 128 ? 16 : 8;
+    const int stage = dim <= 64 ? 32 : (dim <= 128 ? 16 : 8);
 #define DELTA_LAUNCH(N, SL)                                                                                                   \
     do {                                                                                                                      \
         const int cols = DELTA_THREADS / (SL);                                                                                \

@@ -436,8 +436,8 @@ def attention_plain(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pag
         _check(sink32, "sink", torch.float32, 1)
         if sink32.numel() != num_heads:
             raise KernelError("sink must have one entry per query head")
-    if head_dim > 512:
-        raise KernelError(f"plain attention supports head_dim <= 512, got {head_dim}")
+    if head_dim > 1024:
+        raise KernelError(f"plain attention supports head_dim <= 1024, got {head_dim}")
     if num_heads % num_kv_heads:
         raise KernelError("num_heads must be a multiple of num_kv_heads")
     _check(k_pages, "k_pages", q.dtype, 4)
