@@ -58,6 +58,19 @@ KOGO_C = dict(page_size=16, seed=33, cfg=KogonexConfig(
                      None),
     )))
 
+# longer requests: windows of 70 and 130 tokens over pages of 16, attention first and a delta layer last
+KOGO_LONG = dict(page_size=16, seed=44, cfg=KogonexConfig(
+    vocab_size=700, hidden_size=96, norm_eps=1e-5, bigram_buckets=389, bigram_mul_prev=11, bigram_mul_cur=13, layers=(
+        KogonexLayer(LatentAttentionConfig(heads=6, dim=16, rot_dim=32, vdim=24, kv_rank=128, scale=0.12, rot_dims=32,
+                                           rot_base=2e5, scaling=RotaryScaling(16.0, 48, 6.0, 1.5), window=70),
+                     RoutedExpertsConfig(ff=40, experts=10, identity=2, top=3, groups=3, keep=2)),
+        KogonexLayer(LatentAttentionConfig(heads=2, dim=40, rot_dim=32, vdim=56, kv_rank=128, scale=0.1, rot_dims=32,
+                                           rot_base=2e5, scaling=RotaryScaling(16.0, 48, 6.0, 1.5), window=130, kv_from=0),
+                     None),
+        KogonexLayer(ChannelDeltaConfig(heads=4, kv_heads=2, dim=24, vdim=32, conv=3, decay_rank=8, gate_rank=8),
+                     RoutedExpertsConfig(ff=48, experts=4, identity=0, top=2, groups=2, keep=2)),
+    )))
+
 KOGOS = {"kogo_a": KOGO_A, "kogo_b": KOGO_B, "kogo_c": KOGO_C}
 
 

@@ -164,6 +164,27 @@ def test_long_decoding_float32(case):
     check(got, ref, "float32", "long decoding")
 
 
+def test_long_requests_wide_windows_over_pages(tmp_path):
+    """Requests of a few hundred tokens through windows of 70 and 130 over pages of 16: the tensor-core
+    attention walks several blocks of keys whose first and last are cut by the window, the windowed
+    group gives pages back while a request is still fed, and the reader of the shared cache looks
+    further back than the layer that writes it."""
+    from tests.kogonex_tiny import KOGO_LONG
+    tiny = KOGO_LONG
+    reqs = {f"L{i}": random_tokens(n, tiny["cfg"].vocab_size, 600 + i) for i, n in enumerate([330, 260, 150])}
+    cuts = {"whole": traces.whole, "decode_tail": lambda r: traces.decode_tail(r, tail=90),
+            "portions": lambda r: traces.portions(r, sizes=(64, 3, 2, 128, 29, 16, 2, 70)),
+            "mixed": lambda r: traces.mixed(r, max_live=3, seed=5, max_portion=80, stagger=1)}
+    for dtype, decisive in (("float32", False), ("bfloat16", True)):
+        d = make_model_dir(tmp_path / dtype, tiny, decisive=decisive)
+        w = read_weights(d)
+        ref = {rid: plain.forward(tiny["cfg"].to_dict(), w, toks).numpy() for rid, toks in reqs.items()}
+        for cut, build in cuts.items():
+            got, runner = run_cut(tiny, d, build(reqs), dtype)
+            assert len(got) == sum(len(t) for t in reqs.values())
+            check(got, ref, dtype, f"long, {cut}")
+
+
 def follows_plain(cfg, w, prompt, ids, slack):
     logits = plain.forward(cfg.to_dict(), w, ids[:-1])
     return all(float(logits[i - 1].max() - logits[i - 1][ids[i]]) <= slack for i in range(len(prompt), len(ids)))
