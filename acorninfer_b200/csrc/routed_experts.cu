@@ -253,7 +253,7 @@ template <int BM>
 __global__ void __launch_bounds__(256) grouped_gemm_tc_kernel(const bf16* __restrict__ A, int64_t lda,
                                                               const int* __restrict__ a_rows, const bf16* __restrict__ W,
                                                               bf16* __restrict__ C, int64_t ldc,
-                                                              const int* __restrict__ offsets, int E, int N, int K) {
+                                                              const int* __restrict__ offsets, int E, int N, int K, int swiglu) {
     extern __shared__ __align__(16) unsigned char gt_smem[];
     bf16* sA = reinterpret_cast<bf16*>(gt_smem);                               // [STAGES][BM][LDS]
     bf16* sW = sA + GT_STAGES * BM * GT_LDS;                                   // [STAGES][BN][LDS]
@@ -360,6 +360,11 @@ __global__ void __launch_bounds__(256) grouped_gemm_tc_kernel(const bf16* __rest
             for (int nt = 0; nt < NT; ++nt) {
                 const int n = n0 + wn * (GT_BN / WN) + nt * 8 + 2 * t;
                 const float v0 = acc[mt][nt][half * 2], v1 = acc[mt][nt][half * 2 + 1];
+                if (swiglu) {
+                    // weight rows 2i and 2i + 1 are the gate and the up row of output i: both are this thread's
+                    if (n + 1 < N) C[(int64_t)slot * ldc + (n >> 1)] = __float2bfloat16_rn(v0 / (1.f + expf(-v0)) * v1);
+                    continue;
+                }
                 if (n + 1 < N && (ldc & 1) == 0) {
                     *reinterpret_cast<uint32_t*>(C + (int64_t)slot * ldc + n) = pack_bf16(v0, v1);
                 } else {
@@ -373,7 +378,7 @@ __global__ void __launch_bounds__(256) grouped_gemm_tc_kernel(const bf16* __rest
 
 template <int BM>
 static int grouped_gemm_tc_launch(const bf16* A, int64_t lda, const int* a_rows, const bf16* W, bf16* C, int64_t ldc,
-                                  const int* offsets, int slots, int E, int N, int K, cudaStream_t stream) {
+                                  const int* offsets, int slots, int E, int N, int K, int swiglu, cudaStream_t stream) {
     const int64_t tiles = (slots + BM - 1) / BM + E;
     if (tiles > 65535) return ACORN_ERR_UNSUPPORTED;
     const size_t smem = (size_t)GT_STAGES * (BM + GT_BN) * GT_LDS * sizeof(bf16);
@@ -384,19 +389,28 @@ static int grouped_gemm_tc_launch(const bf16* A, int64_t lda, const int* a_rows,
         configured.mark();
     }
     dim3 grid((N + GT_BN - 1) / GT_BN, (unsigned)tiles);
-    return acorn_launch(grouped_gemm_tc_kernel<BM>, grid, dim3(256), smem, stream, A, lda, a_rows, W, C, ldc, offsets, E, N, K);
+    return acorn_launch(grouped_gemm_tc_kernel<BM>, grid, dim3(256), smem, stream, A, lda, a_rows, W, C, ldc, offsets, E, N, K, swiglu);
 }
 
+extern "C" int acorn_grouped_gemm_fuses_swiglu(int N, int K, int64_t lda, int dtype) {
+    return dtype == ACORN_DTYPE_BF16 && K % 8 == 0 && lda % 8 == 0 && N % 2 == 0;
+}
+
+// swiglu: W holds, per output i, the gate row 2i and the up row 2i + 1; C [slots, N / 2] receives
+// silu(gate) * up computed from the float32 sums (tensor-core kernel only: see the query above).
 extern "C" int acorn_grouped_gemm(const void* A, int64_t lda, const int* a_rows, const void* W, void* C, int64_t ldc,
-                                  const int* offsets, int slots, int E, int N, int K, int dtype, cudaStream_t stream) {
+                                  const int* offsets, int slots, int E, int N, int K, int dtype, int swiglu,
+                                  cudaStream_t stream) {
     if (slots <= 0 || E <= 0 || N <= 0) return 0;
+    if (swiglu && !(acorn_grouped_gemm_fuses_swiglu(N, K, lda, dtype) && ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0))
+        return ACORN_ERR_UNSUPPORTED;
     if (dtype == ACORN_DTYPE_BF16 && K % 8 == 0 && lda % 8 == 0 && ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0) {
         // few rows an expert on average: the small tile (a decode step); else the large one
         if ((int64_t)slots <= (int64_t)16 * E)
-            return grouped_gemm_tc_launch<16>((const bf16*)A, lda, a_rows, (const bf16*)W, (bf16*)C, ldc, offsets, slots, E, N, K, stream);
+            return grouped_gemm_tc_launch<16>((const bf16*)A, lda, a_rows, (const bf16*)W, (bf16*)C, ldc, offsets, slots, E, N, K, swiglu, stream);
         if ((int64_t)slots >= (int64_t)256 * E)          // several full tiles an expert: the tall tile (64 x 32 a warp)
-            return grouped_gemm_tc_launch<128>((const bf16*)A, lda, a_rows, (const bf16*)W, (bf16*)C, ldc, offsets, slots, E, N, K, stream);
-        return grouped_gemm_tc_launch<64>((const bf16*)A, lda, a_rows, (const bf16*)W, (bf16*)C, ldc, offsets, slots, E, N, K, stream);
+            return grouped_gemm_tc_launch<128>((const bf16*)A, lda, a_rows, (const bf16*)W, (bf16*)C, ldc, offsets, slots, E, N, K, swiglu, stream);
+        return grouped_gemm_tc_launch<64>((const bf16*)A, lda, a_rows, (const bf16*)W, (bf16*)C, ldc, offsets, slots, E, N, K, swiglu, stream);
     }
     const int64_t tiles = (slots + GG_BM - 1) / GG_BM + E;       // every expert may end in a partly filled tile
     if (tiles > 65535) return ACORN_ERR_UNSUPPORTED;

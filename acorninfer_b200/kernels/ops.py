@@ -121,7 +121,8 @@ class _Sigs:
     acorn_moe_route = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
     acorn_moe_plan = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
     acorn_grouped_gemm = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_int,
-                          c_int, c_int, c_void_p]
+                          c_int, c_int, c_int, c_void_p]
+    acorn_grouped_gemm_fuses_swiglu = [c_int, c_int, c_int64, c_int]
     acorn_moe_combine = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                          c_void_p, c_void_p, c_float, c_void_p]
     acorn_attention_decode = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
@@ -1210,18 +1211,26 @@ def moe_plan(idx: torch.Tensor, num_outputs: int):
     return offsets, slot_of, slot_token
 
 
-def grouped_gemm(a: torch.Tensor, a_rows: torch.Tensor | None, w: torch.Tensor, offsets: torch.Tensor, slots: int) -> torch.Tensor:
+def grouped_gemm(a: torch.Tensor, a_rows: torch.Tensor | None, w: torch.Tensor, offsets: torch.Tensor, slots: int,
+                 swiglu_pairs: bool = False) -> torch.Tensor:
     """out[slot] = a[a_rows[slot]] @ w[e]^T for the slots offsets[e] .. offsets[e + 1] - 1 of every
-    expert e (w [E, N, K]); rows of other slots are left unwritten."""
+    expert e (w [E, N, K]); rows of other slots are left unwritten.  ``swiglu_pairs``: rows 2i and 2i + 1 of
+    ``w[e]`` are the gate and the up row of output i, and what is returned is ``silu(gate) * up``
+    [slots, N / 2]: inside the product's epilogue on the tensor-core kernel, by the SwiGLU kernel after it
+    otherwise."""
     _check(a, "a", None, 2)
     _check(w, "w", a.dtype, 3)
     E, N, K = w.shape
     if a.shape[1] != K:
         raise KernelError(f"grouped_gemm: a {tuple(a.shape)} against w {tuple(w.shape)}")
-    out = torch.empty((slots, N), dtype=a.dtype, device=a.device)
+    fused = swiglu_pairs and a.data_ptr() % 16 == 0 and bool(
+        lib().acorn_grouped_gemm_fuses_swiglu(N, K, a.stride(0), dtype_code(a.dtype)))
+    out = torch.empty((slots, N // 2 if fused else N), dtype=a.dtype, device=a.device)
     _ok(lib().acorn_grouped_gemm(a.data_ptr(), a.stride(0), _ptr(a_rows), w.data_ptr(), out.data_ptr(), out.stride(0),
-                                 offsets.data_ptr(), slots, E, N, K, dtype_code(a.dtype), _stream()), "grouped_gemm",
-        f"{slots}x{N}x{K}")
+                                 offsets.data_ptr(), slots, E, N, K, dtype_code(a.dtype), 1 if fused else 0, _stream()),
+        "grouped_gemm", f"{slots}x{N}x{K}")
+    if swiglu_pairs and not fused:
+        return swiglu(out, block=1)
     return out
 
 

@@ -9,9 +9,10 @@ sum to one).  The last ``identity`` outputs own no tensors and pass their input 
 sum over the chosen.
 
 On the device: the router's choice (one kernel), the (token, choice) pairs grouped by expert (one
-kernel), one product per expert over its own rows for gate/up and for down (a kernel each, walking
-the per-expert offsets on the device: nothing of the routing is read on the host), SwiGLU, and the
-weighted sum in the order of the choices.
+kernel), one product per expert over its own rows for gate/up (SwiGLU in its epilogue on the tensor-core
+kernel) and for down (a kernel each, walking the per-expert offsets on the device: nothing of the routing
+is read on the host), and the weighted sum in the order of the choices, which also norms the result and
+adds it to the stream when the block asks.
 """
 
 from __future__ import annotations
@@ -55,8 +56,10 @@ class RoutedExperts(FeedForward):
         if self.E:
             mats = [t[f"e{e}.{n}"] for e in range(self.E) for n in ("gate", "up", "down")]
             dtype = mats[0].dtype if all(m.dtype == mats[0].dtype for m in mats) else torch.float32
-            self.w_gate_up = torch.stack([torch.cat([t[f"e{e}.gate"].to(dtype), t[f"e{e}.up"].to(dtype)], dim=0)
-                                          for e in range(self.E)]).contiguous()               # [E, 2 ff, width]
+            # gate and up rows in turns (row 2i: gate of output i, row 2i + 1: its up row): a thread of the grouped
+            # product's epilogue then holds both and applies SwiGLU itself
+            self.w_gate_up = torch.stack([torch.stack([t[f"e{e}.gate"].to(dtype), t[f"e{e}.up"].to(dtype)], dim=1)
+                                          .reshape(2 * self.ff, self.hidden_size) for e in range(self.E)]).contiguous()
             self.w_down = torch.stack([t[f"e{e}.down"].to(dtype) for e in range(self.E)]).contiguous()   # [E, width, ff]
 
     adds_normed_residual = True     # ``forward(..., add_normed=(resid32, norm))`` adds the normed result to the stream itself
@@ -70,7 +73,7 @@ class RoutedExperts(FeedForward):
         if self.E:
             w_gu = self.w_gate_up if self.w_gate_up.dtype == x.dtype else self.w_gate_up.to(x.dtype)
             w_dn = self.w_down if self.w_down.dtype == x.dtype else self.w_down.to(x.dtype)
-            hidden = ops.swiglu(ops.grouped_gemm(x, slot_token, w_gu, offsets, slots))
+            hidden = ops.grouped_gemm(x, slot_token, w_gu, offsets, slots, swiglu_pairs=True)
             y = ops.grouped_gemm(hidden, None, w_dn, offsets, slots)
         else:
             y = x

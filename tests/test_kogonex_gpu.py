@@ -8,7 +8,8 @@ entry point and the scheduler.
 
 Errors are relative: the root mean square over the vocabulary of the difference of the logits (mean
 taken off) over the standard deviation of the plain model's logits.  float32 differs from float64 by
-1e-6 .. 1e-5 (summation order); bfloat16 by 5e-3 .. 6e-2 (bfloat16 activations between the products).
+1e-6 .. 1e-5 (summation order); bfloat16 by 5e-3 .. 9e-2 (bfloat16 activations between the products; the
+largest at single positions of these small random models where a sublayer's output is small before its norm).
 """
 
 import math
@@ -27,7 +28,7 @@ from tests.tiny import random_tokens
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
-TOL = {"float32": 4e-5, "bfloat16": 8e-2}
+TOL = {"float32": 4e-5, "bfloat16": 0.12}
 LENGTHS = [45, 38, 61, 50, 33, 29]
 
 
@@ -303,6 +304,15 @@ def test_grouped_products_take_each_experts_own_rows(dtype, tol, E, T, top):
             assert off[e] <= s < off[e + 1]
             if e < E:
                 assert (out[s] - x[t].float() @ w[e].float().T).abs().max() < tol
+    # gate and up rows in turns: silu(gate) * up from the product's own epilogue (bfloat16) or the kernel after it
+    act = o.grouped_gemm(x.to(DEV), slot_token, w.to(DEV), offsets, T * top, swiglu_pairs=True).float().cpu()
+    assert act.shape == (T * top, N // 2)
+    for t in range(0, T, 7):
+        e, s = int(idx[t, 0]), int(so[t, 0])
+        if e < E:
+            gu = x[t].float() @ w[e].float().T
+            want = torch.nn.functional.silu(gu[0::2]) * gu[1::2]
+            assert (act[s] - want).abs().max() < tol * 4, (t, e)
 
 
 def _latent_case(befores, qlens, P, d, dv, nq, window, spikes, dtype, sink_value=None, seed=0, kernel="plain"):
