@@ -162,7 +162,8 @@ extern "C" int acorn_head_linear(const void* x, int64_t xs_t, int64_t xs_h, cons
 // the float32 scores) go to shared memory as bfloat16, the operand of the second product.  Values: the
 // first dv entries of the same key rows; warp (rh, cq) owns 32 rows by a quarter of the dv columns of the
 // float32 accumulator.  Window: query at position p sees keys p - window + 1 .. p.  Sink: exp(sink_h) is
-// added to a row's denominator at the end.
+// added to a row's denominator at the end.  With few tiles (a decode step) the key blocks of a tile are
+// shared out over `splits` blocks, which leave unnormalized sums, maxima and denominators for a merge kernel.
 #define LA_M 64
 #define LA_KB 64
 #define LA_THREADS 256
@@ -173,7 +174,7 @@ __global__ void __launch_bounds__(LA_THREADS) latent_attention_tc_kernel(
     const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ pages, const int* __restrict__ block_table,
     const int* __restrict__ page_base, int table_stride, const int* __restrict__ row_start, const int* __restrict__ row_pos,
     const int* __restrict__ tiles, const float* __restrict__ sink, float scale, int window, int H, int d, int dv, int logP,
-    int kbufs) {
+    int kbufs, int splits, float* __restrict__ part) {
     extern __shared__ __align__(16) unsigned char la_smem[];
     const int lds = d + 8;
     bf16* Qs = reinterpret_cast<bf16*>(la_smem);                 // [64][lds]
@@ -214,7 +215,10 @@ __global__ void __launch_bounds__(LA_THREADS) latent_attention_tc_kernel(
     };
     const int kb_first = (key_lo / LA_KB) * LA_KB;
     const int nblk = (p_last - kb_first) / LA_KB + 1;
-    load_keys(kb_first, 0);
+    // with splits (blockIdx.y), a block takes a contiguous share of the key blocks and leaves partial results
+    const int per = (nblk + splits - 1) / splits;
+    const int it0 = min(nblk, (int)blockIdx.y * per), it1 = min(nblk, it0 + per);
+    if (it0 < it1) load_keys(kb_first + it0 * LA_KB, 0);
     cp_async_commit();
 
     // score phase: rows rg*16 + g and + 8, keys kh*32 ..
@@ -234,10 +238,10 @@ __global__ void __launch_bounds__(LA_THREADS) latent_attention_tc_kernel(
 #pragma unroll
             for (int c = 0; c < 4; ++c) o[mt][nt][c] = 0.f;
 
-    for (int it = 0; it < nblk; ++it) {
+    for (int it = it0; it < it1; ++it) {
         const int kb = kb_first + it * LA_KB;
-        const int buf = kbufs == 2 ? (it & 1) : 0;
-        if (kbufs == 2 && it + 1 < nblk) load_keys(kb + LA_KB, (it + 1) & 1);
+        const int buf = kbufs == 2 ? ((it - it0) & 1) : 0;
+        if (kbufs == 2 && it + 1 < it1) load_keys(kb + LA_KB, (it + 1 - it0) & 1);
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();                                         // this block's keys (and the queries) are here
@@ -337,7 +341,7 @@ __global__ void __launch_bounds__(LA_THREADS) latent_attention_tc_kernel(
             }
         }
         __syncthreads();                                         // the keys' buffer, the weights and the maxima are free
-        if (kbufs == 1 && it + 1 < nblk) {
+        if (kbufs == 1 && it + 1 < it1) {
             load_keys(kb + LA_KB, 0);
             cp_async_commit();
         }
@@ -355,6 +359,30 @@ __global__ void __launch_bounds__(LA_THREADS) latent_attention_tc_kernel(
         }
     }
     __syncthreads();
+    if (splits > 1) {
+        // partial results of this share of the keys: the unnormalized sums, then the row's maximum and denominator
+        float* mine = part + ((int64_t)blockIdx.x * splits + blockIdx.y) * LA_M * (dv + 2);
+        if (threadIdx.x < LA_M) {
+            mine[(int64_t)threadIdx.x * (dv + 2) + dv] = corr_s[threadIdx.x];
+            mine[(int64_t)threadIdx.x * (dv + 2) + dv + 1] = red[threadIdx.x] + red[LA_M + threadIdx.x];
+        }
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int row = rh * 32 + mt * 16 + g + hh * 8;
+                if (row >= rows_valid) continue;
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    const int col = colbase + nt * 8 + 2 * t;
+                    if (col < dv) {
+                        mine[(int64_t)row * (dv + 2) + col] = o[mt][nt][hh * 2];
+                        mine[(int64_t)row * (dv + 2) + col + 1] = o[mt][nt][hh * 2 + 1];
+                    }
+                }
+            }
+        return;
+    }
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt) {
 #pragma unroll
@@ -375,6 +403,39 @@ __global__ void __launch_bounds__(LA_THREADS) latent_attention_tc_kernel(
     }
 }
 
+// One block per (tile, row): the shares' partial results, weighted by exp(their maximum - the common one), over
+// the sum of their denominators and the sink's term.
+__global__ void latent_attention_merge_kernel(const float* __restrict__ part, bf16* __restrict__ out,
+                                              const int* __restrict__ row_start, const int* __restrict__ tiles,
+                                              const float* __restrict__ sink, int H, int dv, int splits) {
+    pdl_wait();
+    pdl_trigger();
+    const int tile = blockIdx.x, row = blockIdx.y;
+    const int r = tiles[2 * tile], q0 = tiles[2 * tile + 1];
+    const int first = row_start[r], len = row_start[r + 1] - first;
+    const int ntok = min(LA_M / H, len - q0);
+    if (row >= ntok * H) return;
+    const float* base = part + (int64_t)tile * splits * LA_M * (dv + 2) + (int64_t)row * (dv + 2);
+    const int64_t stride = (int64_t)LA_M * (dv + 2);
+    float m = -INFINITY;
+    for (int s = 0; s < splits; ++s) m = fmaxf(m, base[s * stride + dv]);
+    float total = sink ? expf(sink[row % H] - m) : 0.f;
+    for (int s = 0; s < splits; ++s) {
+        const float ms = base[s * stride + dv];
+        if (ms > -INFINITY) total += base[s * stride + dv + 1] * expf(ms - m);
+    }
+    const float inv = 1.f / total;
+    bf16* dst = out + ((int64_t)(first + q0) * H + row) * dv;
+    for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float ms = base[s * stride + dv];
+            if (ms > -INFINITY) acc += base[s * stride + c] * expf(ms - m);
+        }
+        dst[c] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
 static size_t latent_tc_smem(int d, int kbufs) {
     return (size_t)(LA_M + kbufs * LA_KB) * (d + 8) * sizeof(bf16) + (size_t)LA_M * LA_PLD * sizeof(bf16) + 3 * LA_M * sizeof(float);
 }
@@ -387,7 +448,8 @@ extern "C" int acorn_latent_attention_tc_supported(int H, int d, int dv, int P) 
 template <int NT>
 static int latent_tc_launch(const bf16* q, bf16* out, const bf16* pages, const int* block_table, const int* page_base,
                             int table_stride, const int* row_start, const int* row_pos, const int* tiles, int num_tiles,
-                            const float* sink, float scale, int window, int H, int d, int dv, int logP, cudaStream_t stream) {
+                            const float* sink, float scale, int window, int H, int d, int dv, int logP, int splits, float* part,
+                            cudaStream_t stream) {
     const int kbufs = latent_tc_smem(d, 2) <= 220 * 1024 ? 2 : 1;
     static AcornPerDevice configured;
     if (!configured.seen()) {
@@ -395,20 +457,24 @@ static int latent_tc_launch(const bf16* q, bf16* out, const bf16* pages, const i
         if (e != cudaSuccess) return (int)e;
         configured.mark();
     }
-    return acorn_launch(latent_attention_tc_kernel<NT>, dim3(num_tiles), dim3(LA_THREADS), latent_tc_smem(d, kbufs), stream, q, out,
-                        pages, block_table, page_base, table_stride, row_start, row_pos, tiles, sink, scale, window, H, d, dv, logP,
-                        kbufs);
+    int rc = acorn_launch(latent_attention_tc_kernel<NT>, dim3(num_tiles, splits), dim3(LA_THREADS), latent_tc_smem(d, kbufs), stream,
+                          q, out, pages, block_table, page_base, table_stride, row_start, row_pos, tiles, sink, scale, window, H, d,
+                          dv, logP, kbufs, splits, part);
+    if (rc != 0 || splits == 1) return rc;
+    return acorn_launch(latent_attention_merge_kernel, dim3(num_tiles, LA_M), dim3(128), 0, stream, (const float*)part, out, row_start,
+                        tiles, sink, H, dv, splits);
 }
 
 extern "C" int acorn_latent_attention_tc(const void* q, void* out, const void* pages, const int* block_table, const int* page_base,
                                          int table_stride, const int* row_start, const int* row_pos, const int* tiles,
                                          int num_tiles, const float* sink, float scale, int window, int H, int d, int dv, int P,
-                                         cudaStream_t stream) {
+                                         int splits, float* part, cudaStream_t stream) {
     if (num_tiles <= 0) return 0;
     if (!acorn_latent_attention_tc_supported(H, d, dv, P)) return ACORN_ERR_UNSUPPORTED;
+    if (splits < 1 || splits > 65535 || (splits > 1 && part == nullptr)) return ACORN_ERR_UNSUPPORTED;
     const int logP = acorn_log2_exact(P);
 #define LA_ARGS (const bf16*)q, (bf16*)out, (const bf16*)pages, block_table, page_base, table_stride, row_start, row_pos, tiles, \
-                num_tiles, sink, scale, window, H, d, dv, logP, stream
+                num_tiles, sink, scale, window, H, d, dv, logP, splits, part, stream
     if (dv <= 64) return latent_tc_launch<2>(LA_ARGS);
     if (dv <= 128) return latent_tc_launch<4>(LA_ARGS);
     if (dv <= 256) return latent_tc_launch<8>(LA_ARGS);

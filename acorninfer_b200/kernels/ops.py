@@ -106,7 +106,7 @@ class _Sigs:
                          c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                          c_int, c_void_p]
     acorn_latent_attention_tc = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                                 c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p]
+                                 c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
     acorn_latent_attention_tc_supported = [c_int, c_int, c_int, c_int]
     acorn_head_linear = [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int,
                          c_int, c_void_p]
@@ -1069,10 +1069,12 @@ def latent_attention_tc_supported(dtype: torch.dtype, num_heads: int, head_dim: 
 
 def latent_attention_tc(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor, page_base: torch.Tensor,
                         row_start: torch.Tensor, row_pos: torch.Tensor, tiles: torch.Tensor, sink32: torch.Tensor | None,
-                        scale: float, window: int | None, value_dim: int) -> torch.Tensor:
+                        scale: float, window: int | None, value_dim: int, splits: int | None = None) -> torch.Tensor:
     """Attention of q [T, H, d] (bfloat16) over one cached row of d per token (pages [pages, 1, P, d]) whose
     first ``value_dim`` entries are the values: returns [T, H, value_dim].  ``tiles`` int32 [n, 2]: (row, first
-    token within the row) of every group of ``LATENT_TILE_ROWS // H`` tokens."""
+    token within the row) of every group of ``LATENT_TILE_ROWS // H`` tokens.  ``splits``: blocks that share a
+    tile's keys (None: as many as fill the device when tiles are few, by the table's width and the window, so
+    that a captured step keeps its grid)."""
     _check(q, "q", torch.bfloat16, 3)
     _check(pages, "pages", torch.bfloat16, 4)
     _check(tiles, "tiles", torch.int32, 2)
@@ -1082,10 +1084,17 @@ def latent_attention_tc(q: torch.Tensor, pages: torch.Tensor, block_table: torch
     if sink32 is not None:
         _check(sink32, "sink", torch.float32, 1)
     out = torch.empty((T, H, value_dim), dtype=torch.bfloat16, device=q.device)
+    n = tiles.shape[0]
+    if splits is None:
+        bound = block_table.shape[1] * pages.shape[2]
+        if window:
+            bound = min(bound, int(window) + LATENT_TILE_ROWS)
+        splits = max(1, min(-(-device_sms(q.device) // max(n, 1)), -(-bound // 64), 32)) if n * 2 <= device_sms(q.device) else 1
+    part = torch.empty((n, splits, LATENT_TILE_ROWS, value_dim + 2), dtype=torch.float32, device=q.device) if splits > 1 else None
     _ok(lib().acorn_latent_attention_tc(q.data_ptr(), out.data_ptr(), pages.data_ptr(), block_table.data_ptr(),
                                         page_base.data_ptr(), block_table.stride(0), row_start.data_ptr(), row_pos.data_ptr(),
-                                        tiles.data_ptr(), tiles.shape[0], _ptr(sink32), float(scale), int(window or 0), H, d,
-                                        int(value_dim), pages.shape[2], _stream()), "latent_attention_tc")
+                                        tiles.data_ptr(), n, _ptr(sink32), float(scale), int(window or 0), H, d,
+                                        int(value_dim), pages.shape[2], int(splits), _ptr(part), _stream()), "latent_attention_tc")
     return out
 
 

@@ -346,9 +346,12 @@ def _latent_case(befores, qlens, P, d, dv, nq, window, spikes, dtype, sink_value
         n = o.LATENT_TILE_ROWS // nq
         i32 = dict(dtype=torch.int32, device=DEV)
         tiles = torch.tensor([(r, q0) for r, length in enumerate(qlens) for q0 in range(0, length, n)], **i32)
-        out = o.latent_attention_tc(q_new, pages, lay["block_table"], lay["page_base"],
-                                    torch.tensor(np.cumsum([0] + qlens), **i32), torch.tensor(befores, **i32), tiles,
-                                    None if sink is None else sink.to(DEV), scale, window, dv).float().cpu()
+        args = (q_new, pages, lay["block_table"], lay["page_base"], torch.tensor(np.cumsum([0] + qlens), **i32),
+                torch.tensor(befores, **i32), tiles, None if sink is None else sink.to(DEV), scale, window, dv)
+        out = o.latent_attention_tc(*args).float().cpu()
+        for splits in (1, 3, 7):              # a tile's key blocks shared out over several blocks and merged
+            again = o.latent_attention_tc(*args, splits=splits).float().cpu()
+            assert (again - out).abs().max() < 2e-2, splits
     else:
         out = ops().attention_plain(q_new.view(-1, nq * d), nq * d, pages, pages, lay["block_table"], lay["page_base"],
                                     lay["token_row"], lay["positions"], lay["num_tokens"], nq, 1, d, scale, window,
