@@ -8,11 +8,11 @@ command line, ``bin/trace_run`` the trace replay.
 """
 
 from .config.engine_config import EngineConfig  # noqa: F401
-from .config.model_config import ConfigError, ModelConfig, Qwen3Config  # noqa: F401
+from .config.model_config import ConfigError, KogonexConfig, ModelConfig, Qwen3Config  # noqa: F401
 from .registry import known_architectures, load_config, register_architecture  # noqa: F401
 from .sampling.params import SamplingParams  # noqa: F401
 
-__all__ = ["EngineConfig", "ConfigError", "ModelConfig", "Qwen3Config", "SamplingParams", "generate", "Engine",
+__all__ = ["EngineConfig", "ConfigError", "ModelConfig", "Qwen3Config", "KogonexConfig", "SamplingParams", "generate", "Engine",
            "ModelRunner", "register_architecture", "known_architectures", "load_config"]
 
 

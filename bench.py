@@ -12,6 +12,10 @@ step.  ``prefill`` is one 2,048-token prompt in one step; ``points`` are decode 
 the cache of the live requests) with the measured copy bandwidth.  Weights are random
 (seeded N(0, 0.02), norms 1), token ids uniform random: synthetic data.  Weights
 (15 GB) are far larger than L2, so no L2 flush is needed between steps.
+
+``--design kogonex`` is another workload and prints another line: prefill and decode of the Kogonex
+architecture at two sets of layer sizes beside Qwen3 dense of equal width, depth, vocabulary and active
+feed-forward width, with the device time of every kernel of one prefill and one decode step.
 """
 
 from __future__ import annotations
