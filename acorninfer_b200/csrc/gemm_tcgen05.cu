@@ -36,6 +36,7 @@ __device__ int g_gemm_tc_error = 0;
 #define TC_MODE_ADD_NORM 1    // residual += product; out = bf16(residual * norm_w); ss_out = partial sum of squares
 #define TC_MODE_SWIGLU 2      // tiles of 64 gate + 64 up columns: out = silu(gate) * up
 #define TC_MODE_QKV_ROPE 3    // tiles are heads of 128: q/k RMSNorm + rotation; k and v to their cache pages
+#define TC_MODE_SWIGLU_PAIRS 4   // columns 2i and 2i + 1 are the gate and the up value of output i
 // reduction scratch of the epilogues (floats): four partial sums a row, or a head and its partial sums
 #define TC_RED_FLOATS(MB) (4 * (MB) > 256 ? 4 * (MB) : 256)
 
@@ -68,6 +69,11 @@ struct TcParams {
     bf16* v_pages;           // nullptr: keys and values are not written (a layer that reads another's cache)
     int table_stride, nq, nkv, logP;
     float rope_eps;
+    // A product per expert (g_offsets != nullptr): rows g_offsets[e] .. g_offsets[e + 1] - 1 of x belong to expert e,
+    // whose matrix is rows e * N .. of W ([g_experts * N, K]); blockIdx.y counts the token tiles of all experts in
+    // turn (at most g_tiles; a CTA beyond the last one leaves at once).  K is not split.
+    const int* g_offsets;
+    int g_experts, g_tiles;
 };
 
 // A load that the compiler leaves where it is written (it may not sink it below a barrier to the
@@ -99,7 +105,24 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
     const uint32_t full0 = tc_smem(bars), empty0 = tc_smem(bars + STAGES), accum_bar = tc_smem(bars + 2 * STAGES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * TC_BM, m0 = blockIdx.y * MB;
+    const int n0 = blockIdx.x * TC_BM;
+    int m0 = blockIdx.y * MB, m_end = p.M, w_row0 = n0;
+    if (p.g_offsets != nullptr) {
+        pdl_wait();                                      // the offsets are the work of the kernel before this one
+        int tile = blockIdx.y, found = -1;
+        for (int e = 0; e < p.g_experts; ++e) {
+            const int tiles = (p.g_offsets[e + 1] - p.g_offsets[e] + MB - 1) / MB;
+            if (tile < tiles) {
+                found = e;
+                break;
+            }
+            tile -= tiles;
+        }
+        if (found < 0) return;                           // nothing is set up yet: no barrier, no tensor memory
+        m0 = p.g_offsets[found] + tile * MB;
+        m_end = p.g_offsets[found + 1];
+        w_row0 = found * p.N + n0;
+    }
     const int splits = gridDim.z, split = blockIdx.z;
     const int kb0 = (int)((int64_t)p.kblocks * split / splits), kb1 = (int)((int64_t)p.kblocks * (split + 1) / splits);
     const int nkb = kb1 - kb0;
@@ -125,7 +148,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
         for (int i = 0; i < pre; ++i) {
             if (elect_one()) {
                 mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
-                tma_load_2d(tc_smem(smem + i * STAGE_BYTES), &map_w, full0 + 8 * i, (kb0 + i) * TC_BK, n0);
+                tma_load_2d(tc_smem(smem + i * STAGE_BYTES), &map_w, full0 + 8 * i, (kb0 + i) * TC_BK, w_row0);
             }
         }
     }
@@ -155,7 +178,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
             if (elect_one()) {
                 mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
                 const uint32_t a = tc_smem(smem + s * STAGE_BYTES);
-                tma_load_2d(a, &map_w, full0 + 8 * s, (kb0 + i) * TC_BK, n0);
+                tma_load_2d(a, &map_w, full0 + 8 * s, (kb0 + i) * TC_BK, w_row0);
                 tma_load_2d(a + A_BYTES, &map_x, full0 + 8 * s, (kb0 + i) * TC_BK, m0);
             }
         }
@@ -187,7 +210,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
     ok = __all_sync(0xffffffffu, ok);               // tcgen05.ld below is warp-wide
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int n = n0 + warp * 32 + lane;
-    const int m_valid = min(MB, p.M - m0);
+    const int m_valid = min(MB, m_end - m0);
     const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
 
     // The output tile is finished by rows: row m by the CTA of rank m % csize of the cluster (all
@@ -300,6 +323,15 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
                         __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
             }
         }
+    } else if (p.mode == TC_MODE_SWIGLU_PAIRS) {
+        // gate and up columns in turns: the thread of an even column takes both
+        for (int i = 0, m = rank; m < m_valid; ++i, m += csize) {
+            if ((col & 1) == 0 && n0 + col + 1 < p.N) {
+                const float g = tile_sum(i, col) * inv_s[m], u = tile_sum(i, col + 1) * inv_s[m];
+                reinterpret_cast<bf16*>(p.out)[(int64_t)(m0 + m) * p.ldo + ((n0 + col) >> 1)] =
+                    __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
+            }
+        }
     } else if (p.mode == TC_MODE_QKV_ROPE) {
         // The tile is one head.  Query and key heads: RMSNorm over the head (float32, on the
         // accumulator: no rounding in between), then the rotation of (x[j], x[j + 64]) by
@@ -399,7 +431,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParam
         configured.mark();
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((p.N + TC_BM - 1) / TC_BM, (p.M + MB - 1) / MB, splits);
+    cfg.gridDim = dim3((p.N + TC_BM - 1) / TC_BM, p.g_offsets != nullptr ? p.g_tiles : (p.M + MB - 1) / MB, splits);
     cfg.blockDim = dim3(TC_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
@@ -484,6 +516,30 @@ extern "C" int acorn_gemm_tc_qkv_rope(const void* x, int64_t ldx, const void* w,
     p.table_stride = table_stride; p.k_pages = (bf16*)k_pages; p.v_pages = (bf16*)v_pages; p.q_w = q_w; p.k_w = k_w;
     p.inv_freq = inv_freq; p.nq = nq; p.nkv = nkv; p.logP = logP; p.rope_eps = rope_eps;
     return run_tc(x, ldx, w, ldw, p, splits, per_sm, stream);
+}
+
+// A product per expert on tiles of 128 rows: x [slots, K] holds every expert's rows together (offsets [E + 1]),
+// w [E, N, K] contiguous, out [slots, N] or, with swiglu_pairs (weight rows 2i / 2i + 1 = gate / up of output i),
+// silu(gate) * up [slots, N / 2].  Rows beyond an expert's last one in its last tile are computed and not stored.
+extern "C" int acorn_grouped_gemm_tcgen05(const void* x, int64_t ldx, const void* w, void* out, int64_t ldo,
+                                          const int* offsets, int slots, int E, int N, int K, int swiglu_pairs,
+                                          cudaStream_t stream) {
+    if (slots <= 0 || E <= 0 || N <= 0) return 0;
+    if (!acorn_gemm_tc_supported(slots, N, K, ldx, K) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return ACORN_ERR_UNSUPPORTED;
+    if (swiglu_pairs && N % 2) return ACORN_ERR_UNSUPPORTED;
+    const int64_t tiles = (slots + 127) / 128 + E;
+    if (tiles > 65535 || (int64_t)E * N > 0x7fffffff) return ACORN_ERR_UNSUPPORTED;
+    TcParams p = {};
+    p.out = out; p.ldo = ldo; p.M = slots; p.N = N; p.K = K; p.out_f32 = 0;
+    p.mode = swiglu_pairs ? TC_MODE_SWIGLU_PAIRS : TC_MODE_PLAIN;
+    p.g_offsets = offsets; p.g_experts = E; p.g_tiles = (int)tiles;
+    p.kblocks = (K + TC_BK - 1) / TC_BK;
+    CUtensorMap mw, mx;
+    int rc = make_map(&mw, w, (int64_t)E * N, K, K, TC_BK, TC_BM);
+    if (rc) return rc;
+    rc = make_map(&mx, x, slots, K, ldx, TC_BK, 128);
+    if (rc) return rc;
+    return launch_tc<128, 3>(mw, mx, p, 1, stream);
 }
 
 extern "C" int acorn_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw, void* out, int64_t ldo, int M,

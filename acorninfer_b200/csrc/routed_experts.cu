@@ -155,6 +155,31 @@ extern "C" int acorn_moe_plan(const int* idx, int* offsets, int* slot_of, int* s
                         slot_token, pairs, N, top);
 }
 
+// out[i, :] = x[rows[i], :]: the tokens' rows in the order of the slots, for a product whose operand tiles are
+// fetched by TMA (contiguous rows).  16 bytes a thread and step when the rows allow it.
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ rows, T* __restrict__ out, int H) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t i = blockIdx.x;
+    const T* src = x + (int64_t)rows[i] * H;
+    T* dst = out + i * H;
+    constexpr int EPC = 16 / (int)sizeof(T);
+    if (H % EPC == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+        for (int c = threadIdx.x; c < H / EPC; c += blockDim.x)
+            reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(src)[c];
+    } else {
+        for (int c = threadIdx.x; c < H; c += blockDim.x) dst[c] = src[c];
+    }
+}
+
+extern "C" int acorn_gather_rows(const void* x, const int* rows, void* out, int n, int H, int dtype, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(gather_rows_kernel<T>, dim3(n), dim3(128), 0, stream, (const T*)x, rows,
+                                                       (T*)out, H));
+    return ACORN_ERR_UNSUPPORTED;
+}
+
 // ---------------------------------------------------------------- a product per expert
 // Slots offsets[e] .. offsets[e+1]-1 belong to expert e.  Row `slot` of A is a_rows ? A[a_rows[slot]] : A[slot].
 // A block finds its (expert, tile of GG_BM slots) by walking the offsets; blocks beyond the last tile

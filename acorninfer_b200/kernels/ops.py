@@ -123,6 +123,9 @@ class _Sigs:
     acorn_grouped_gemm = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_int,
                           c_int, c_int, c_int, c_void_p]
     acorn_grouped_gemm_fuses_swiglu = [c_int, c_int, c_int64, c_int]
+    acorn_grouped_gemm_tcgen05 = [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                  c_void_p]
+    acorn_gather_rows = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
     acorn_moe_combine = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                          c_void_p, c_void_p, c_float, c_void_p]
     acorn_attention_decode = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
@@ -1220,6 +1223,9 @@ def moe_plan(idx: torch.Tensor, num_outputs: int):
     return offsets, slot_of, slot_token
 
 
+GROUPED_TCGEN05_MIN_ROWS = 64      # rows an expert on average from which the grouped product takes the tcgen05 kernel
+
+
 def grouped_gemm(a: torch.Tensor, a_rows: torch.Tensor | None, w: torch.Tensor, offsets: torch.Tensor, slots: int,
                  swiglu_pairs: bool = False) -> torch.Tensor:
     """out[slot] = a[a_rows[slot]] @ w[e]^T for the slots offsets[e] .. offsets[e + 1] - 1 of every
@@ -1234,6 +1240,21 @@ def grouped_gemm(a: torch.Tensor, a_rows: torch.Tensor | None, w: torch.Tensor, 
         raise KernelError(f"grouped_gemm: a {tuple(a.shape)} against w {tuple(w.shape)}")
     fused = swiglu_pairs and a.data_ptr() % 16 == 0 and bool(
         lib().acorn_grouped_gemm_fuses_swiglu(N, K, a.stride(0), dtype_code(a.dtype)))
+    if (a.dtype == torch.bfloat16 and slots >= GROUPED_TCGEN05_MIN_ROWS * E and K % 8 == 0 and a.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and (N % 2 == 0 or not swiglu_pairs)):
+        # many rows an expert (a prompt's step): tiles of 128 rows on the tcgen05 kernel, operand tiles by TMA, which
+        # wants an expert's rows next to one another: the tokens' rows are first copied into slot order
+        if a_rows is not None:
+            rows_in = torch.empty((slots, K), dtype=a.dtype, device=a.device)
+            _ok(lib().acorn_gather_rows(a.data_ptr(), a_rows.data_ptr(), rows_in.data_ptr(), slots, K, dtype_code(a.dtype),
+                                        _stream()), "gather_rows")
+        else:
+            rows_in = a
+        out = torch.empty((slots, N // 2 if swiglu_pairs else N), dtype=a.dtype, device=a.device)
+        _ok(lib().acorn_grouped_gemm_tcgen05(rows_in.data_ptr(), rows_in.stride(0), w.data_ptr(), out.data_ptr(), out.stride(0),
+                                             offsets.data_ptr(), slots, E, N, K, 1 if swiglu_pairs else 0, _stream()),
+            "grouped_gemm_tcgen05", f"{slots}x{N}x{K}")
+        return out
     out = torch.empty((slots, N // 2 if fused else N), dtype=a.dtype, device=a.device)
     _ok(lib().acorn_grouped_gemm(a.data_ptr(), a.stride(0), _ptr(a_rows), w.data_ptr(), out.data_ptr(), out.stride(0),
                                  offsets.data_ptr(), slots, E, N, K, dtype_code(a.dtype), 1 if fused else 0, _stream()),

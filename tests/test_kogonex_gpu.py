@@ -281,12 +281,15 @@ def test_router_choice_matches_plain(N, top, groups, keep):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.bfloat16, 0.15)])
-@pytest.mark.parametrize("E,T,top", [(7, 90, 2), (2, 300, 2), (12, 5, 2)])
-def test_grouped_products_take_each_experts_own_rows(dtype, tol, E, T, top):
+@pytest.mark.parametrize("E,T,top,min_rows", [(7, 90, 2, None), (2, 300, 2, None), (12, 5, 2, None), (3, 400, 2, 10 ** 9)])
+def test_grouped_products_take_each_experts_own_rows(dtype, tol, E, T, top, min_rows, monkeypatch):
     """Rows scattered over experts, some experts with no rows and some with more than a tile: every
-    row against its own expert's matrix.  The three shapes take the three tile heights of the
-    tensor-core kernel in bfloat16 (64, 128 and 16 slots)."""
+    row against its own expert's matrix.  In bfloat16 the second shape has enough rows an expert for the
+    tcgen05 kernel (tiles of 128 rows, an expert's last tile partly another's rows); the others, and the
+    last with that kernel switched off, take the three tile heights of the mma.sync kernel (64, 16, 128)."""
     o = ops()
+    if min_rows is not None:
+        monkeypatch.setattr(o, "GROUPED_TCGEN05_MIN_ROWS", min_rows)
     g = torch.Generator().manual_seed(2)
     N, K = 50, 40
     idx = torch.randint(0, E + 2, (T, top), generator=g, dtype=torch.int32)       # two more outputs: identity experts
