@@ -37,6 +37,7 @@ class CacheGroup:
     entries: list[int]                  # schedule entries whose cache lives here, in order
     pool: IdPool
     storage: object = None              # torch tensor [len(entries), 2, pages, nkv, P, d] or None
+    value_storage: object = None        # [len(entries), pages, nkv, P, dv] where values have a width of their own
 
     @property
     def window(self) -> int | None:
@@ -103,8 +104,12 @@ class CacheManager:
             import torch
             for g in self.groups:
                 n = g.needs
-                g.storage = torch.zeros((len(g.entries), 2 if n.values else 1, g.pool.total + 1, n.num_kv_heads, page_size, n.head_dim),
-                                        dtype=n.dtype or dtype, device=device)
+                own_values = n.values and n.value_width != n.head_dim
+                g.storage = torch.zeros((len(g.entries), 2 if (n.values and not own_values) else 1, g.pool.total + 1,
+                                         n.num_kv_heads, page_size, n.head_dim), dtype=n.dtype or dtype, device=device)
+                if own_values:
+                    g.value_storage = torch.zeros((len(g.entries), g.pool.total + 1, n.num_kv_heads, page_size,
+                                                   n.value_width), dtype=n.dtype or dtype, device=device)
             for entry, sn in self.state_needs.items():
                 self.state[entry] = torch.zeros((num_slots + 1, *sn.shape), dtype=sn.dtype or torch.float32,
                                                 device=device)
@@ -116,6 +121,8 @@ class CacheManager:
         group that keeps one row per token only."""
         gi, li = self.entry_group[entry]
         st = self.groups[gi].storage
+        if self.groups[gi].value_storage is not None:
+            return st[li, 0], self.groups[gi].value_storage[li]
         return st[li, 0], (st[li, 1] if st.shape[1] > 1 else None)
 
     def group_of(self, entry: int) -> int:
@@ -125,7 +132,8 @@ class CacheManager:
         total = 0
         for g in self.groups:
             width = 2 if g.storage is None else g.storage.element_size()
-            total += len(g.entries) * (2 if g.needs.values else 1) * g.needs.num_kv_heads * g.needs.head_dim * width
+            per_head = g.needs.head_dim + (g.needs.value_width if g.needs.values else 0)
+            total += len(g.entries) * g.needs.num_kv_heads * per_head * width
         return total
 
     # ------------------------------------------------------------------ requests
@@ -142,9 +150,15 @@ class CacheManager:
 
     def _first_needed_page(self, g: CacheGroup, length: int) -> int:
         """Logical index of the first page a query at position >= ``length`` can still read."""
-        if g.window is None:
+        n = g.needs
+        if n.keep_first > 0:                    # the first keys stay readable: no page of the front is given back
             return 0
-        return max(0, (length - g.window + 1) // self.page_size)
+        first = 0
+        if n.window is not None:
+            first = max(0, length - n.window + 1)
+        if n.chunk is not None:
+            first = max(first, length - length % n.chunk)
+        return first // self.page_size
 
     def pages_needed(self, rc: RequestCache | None, new_length: int) -> list[int]:
         """Per group, the pages to add so that a step can bring the request to ``new_length``."""
@@ -159,11 +173,12 @@ class CacheManager:
         out = []
         for g in self.groups:
             full = ceil_div(total_length, self.page_size)
-            if g.window is None:
+            spans = [s for s in (g.needs.window, g.needs.chunk) if s is not None]
+            if not spans or g.needs.keep_first > 0:
                 out.append(full)
             else:
                 portion = total_length if max_portion is None else min(max_portion, total_length)
-                out.append(min(full, ceil_div(g.window + portion, self.page_size) + 1))
+                out.append(min(full, ceil_div(min(spans) + portion, self.page_size) + 1))
         return out
 
     def free_pages(self) -> list[int]:

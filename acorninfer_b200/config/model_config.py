@@ -396,6 +396,207 @@ class KogonexConfig(ModelConfig):
         return out
 
 
+# --------------------------------------------------------------------------- Vagulorn
+
+
+@dataclass(frozen=True)
+class MaskedAttentionConfig:
+    """Grouped-query attention with q/k norm and rotary positions on the first ``rot_dims`` entries of a head.
+    ``mask_size`` None: every earlier key is read; else the rule its place in the model gives it (blocks of
+    positions for a layer of its own, a window with ``keep_first`` kept keys beside a recurrent mixer)."""
+
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    rot_dims: int = 0
+    rot_base: float = 10000.0
+    mask_size: int | None = None
+    keep_first: int = 0
+
+    @classmethod
+    def from_dict(cls, m: dict, where: str) -> "MaskedAttentionConfig":
+        rot = _sub(m, "rot", where, required=False)
+        mask = _sub(m, "mask", where, required=False)
+        return cls(heads=_take(m, "heads", int), kv_heads=_take(m, "kv_heads", int), dim=_take(m, "dim", int),
+                   vdim=_take(m, "vdim", int), scale=_take(m, "scale", float),
+                   rot_dims=0 if rot is None else _take(rot, "dims", int),
+                   rot_base=10000.0 if rot is None else _take(rot, "base", float),
+                   mask_size=None if mask is None else _take(mask, "size", int, None),
+                   keep_first=0 if mask is None else _take(mask, "keep_first", int, 0))
+
+    def check(self, where: str) -> None:
+        if min(self.heads, self.kv_heads, self.dim, self.vdim) < 1 or self.heads % self.kv_heads:
+            raise ConfigError(f"config.json: {where}sizes must be >= 1 and 'heads' a multiple of 'kv_heads'")
+        if self.rot_dims % 2 or not (0 <= self.rot_dims <= self.dim):
+            raise ConfigError(f"config.json: {where}rot.dims must be even and at most dim, got {self.rot_dims}")
+        if self.rot_dims and not self.rot_base > 0:
+            raise ConfigError(f"config.json: {where}rot.base must be > 0, got {self.rot_base}")
+        if self.mask_size is not None and self.mask_size < 1:
+            raise ConfigError(f"config.json: {where}mask.size must be >= 1, got {self.mask_size}")
+        if self.keep_first < 0:
+            raise ConfigError(f"config.json: {where}mask.keep_first must be >= 0, got {self.keep_first}")
+
+    def to_dict(self) -> dict:
+        out: dict = {"dim": self.dim, "heads": self.heads, "kv_heads": self.kv_heads, "scale": self.scale, "vdim": self.vdim}
+        if self.rot_dims:
+            out["rot"] = {"base": self.rot_base, "dims": self.rot_dims}
+        if self.mask_size is not None:
+            out["mask"] = {"size": self.mask_size}
+            if self.keep_first:
+                out["mask"]["keep_first"] = self.keep_first
+        return out
+
+
+@dataclass(frozen=True)
+class DecayLinearAttentionConfig:
+    """Linear attention with one fixed decay per head."""
+
+    heads: int
+    dim: int
+    vdim: int
+    decay: tuple[float, ...]
+
+    @classmethod
+    def from_dict(cls, m: dict, where: str) -> "DecayLinearAttentionConfig":
+        decay = m.get("decay")
+        if not isinstance(decay, list) or not all(isinstance(d, (int, float)) and not isinstance(d, bool) for d in decay):
+            raise ConfigError(f"config.json: {where}'decay' must be a list of numbers, one per head")
+        return cls(heads=_take(m, "heads", int), dim=_take(m, "dim", int), vdim=_take(m, "vdim", int),
+                   decay=tuple(float(d) for d in decay))
+
+    def check(self, where: str) -> None:
+        if min(self.heads, self.dim, self.vdim) < 1 or len(self.decay) != self.heads:
+            raise ConfigError(f"config.json: {where}sizes must be >= 1 and 'decay' hold one number per head")
+
+    def to_dict(self) -> dict:
+        return {"decay": list(self.decay), "dim": self.dim, "heads": self.heads, "vdim": self.vdim}
+
+
+@dataclass(frozen=True)
+class SideBySideConfig:
+    """Attention (left) and linear attention (right) on the same input, their results scaled and added."""
+
+    left: MaskedAttentionConfig
+    right: DecayLinearAttentionConfig
+    left_scale: float
+    right_scale: float
+
+    @classmethod
+    def from_dict(cls, m: dict, where: str) -> "SideBySideConfig":
+        return cls(left=MaskedAttentionConfig.from_dict(_sub(m, "left", where), where + "left."),
+                   right=DecayLinearAttentionConfig.from_dict(_sub(m, "right", where), where + "right."),
+                   left_scale=_take(m, "left_scale", float), right_scale=_take(m, "right_scale", float))
+
+    def check(self, where: str) -> None:
+        self.left.check(where + "left.")
+        self.right.check(where + "right.")
+        if self.left.vdim != self.left.dim:
+            raise ConfigError(f"config.json: {where}left.vdim must equal left.dim (the values are the keys)")
+
+    def to_dict(self) -> dict:
+        return {"left": self.left.to_dict(), "left_scale": self.left_scale, "right": self.right.to_dict(),
+                "right_scale": self.right_scale}
+
+
+@dataclass(frozen=True)
+class StateSpaceConfig:
+    """A selective state space layer (state-space duality form)."""
+
+    heads: int
+    vdim: int
+    state: int
+    groups: int
+    conv: int
+    norm_groups: int
+
+    @classmethod
+    def from_dict(cls, m: dict, where: str) -> "StateSpaceConfig":
+        return cls(heads=_take(m, "heads", int), vdim=_take(m, "vdim", int), state=_take(m, "state", int),
+                   groups=_take(m, "groups", int), conv=_take(m, "conv", int), norm_groups=_take(m, "norm_groups", int))
+
+    def check(self, where: str) -> None:
+        if min(self.heads, self.vdim, self.state, self.groups, self.conv, self.norm_groups) < 1:
+            raise ConfigError(f"config.json: {where}sizes must be >= 1")
+        if self.heads % self.groups or (self.heads * self.vdim) % self.norm_groups:
+            raise ConfigError(f"config.json: {where}'groups' must divide 'heads' and 'norm_groups' must divide heads * vdim")
+
+    def to_dict(self) -> dict:
+        return {"conv": self.conv, "groups": self.groups, "heads": self.heads, "norm_groups": self.norm_groups,
+                "state": self.state, "vdim": self.vdim}
+
+
+_VAGULORN_MIXERS = {"attention": MaskedAttentionConfig, "parallel": SideBySideConfig, "mamba2": StateSpaceConfig}
+
+
+@dataclass(frozen=True)
+class VagulornLayer:
+    type: str                   # "attention", "parallel" or "mamba2"
+    mixer: MaskedAttentionConfig | SideBySideConfig | StateSpaceConfig
+    ff: int | None              # inner width of the dense gated feed-forward; None: the layer has none
+
+
+@dataclass(frozen=True)
+class VagulornConfig(ModelConfig):
+    """Vagulorn: token rows times a scale; layers ``h = LayerNorm(x); x += mixer(h) + ff(h)`` whose mixer is
+    attention within blocks of positions, attention with a window and kept first keys beside linear attention
+    with fixed decays, or a selective state space layer, and whose feed-forward is gated with the tanh form of
+    gelu (or absent); a final LayerNorm and the token table as output matrix.  ``config.json`` lists the layers in
+    order, each with its own sizes."""
+
+    architecture: ClassVar[str] = "Vagulorn"
+
+    vocab_size: int
+    hidden_size: int
+    norm_eps: float
+    embedding_scale: float
+    layers: tuple[VagulornLayer, ...]
+    eos_token_id: tuple[int, ...] = field(default_factory=tuple)
+
+    def __post_init__(self) -> None:
+        if self.vocab_size < 1 or self.hidden_size < 1 or not self.layers:
+            raise ConfigError("config.json: 'vocab', 'width' must be >= 1 and 'layers' non-empty")
+        if not self.norm_eps > 0:
+            raise ConfigError(f"config.json: norm 'eps' must be > 0, got {self.norm_eps}")
+        for i, layer in enumerate(self.layers):
+            layer.mixer.check(f"layers[{i}].mixer.")
+            if layer.ff is not None and layer.ff < 1:
+                raise ConfigError(f"config.json: layers[{i}].mlp.ff must be >= 1, got {layer.ff}")
+
+    @classmethod
+    def from_dict(cls, raw: dict) -> "VagulornConfig":
+        layers_raw = raw.get("layers")
+        if not isinstance(layers_raw, list) or not layers_raw:
+            raise ConfigError("config.json: 'layers' must be a non-empty list")
+        layers = []
+        for i, lr in enumerate(layers_raw):
+            where = f"layers[{i}]."
+            kind = lr.get("type") if isinstance(lr, dict) else None
+            if kind not in _VAGULORN_MIXERS:
+                raise ConfigError(f"config.json: {where}'type' must be one of {sorted(_VAGULORN_MIXERS)}, got {kind!r}")
+            mixer = _VAGULORN_MIXERS[kind].from_dict(_sub(lr, "mixer", where), where + "mixer.")
+            mlp = _sub(lr, "mlp", where, required=False)
+            if mlp is not None and mlp.get("kind", "dense") != "dense":
+                raise ConfigError(f"config.json: {where}mlp.kind must be 'dense', got {mlp.get('kind')!r}")
+            layers.append(VagulornLayer(kind, mixer, None if mlp is None else _take(mlp, "ff", int)))
+        emb = _sub(raw, "embedding", "", required=False) or {}
+        eos = raw.get("eos_token_id")
+        eos_ids = () if eos is None else tuple(int(e) for e in (eos if isinstance(eos, (list, tuple)) else [eos]))
+        return cls(vocab_size=_take(raw, "vocab", int), hidden_size=_take(raw, "width", int),
+                   norm_eps=_take(_sub(raw, "norm", ""), "eps", float),
+                   embedding_scale=_take(emb, "scale", float, 1.0), layers=tuple(layers), eos_token_id=eos_ids)
+
+    def to_dict(self) -> dict:
+        out: dict = {"architecture": self.architecture, "vocab": self.vocab_size, "width": self.hidden_size,
+                     "norm": {"eps": self.norm_eps}, "embedding": {"scale": self.embedding_scale}}
+        out["layers"] = [{"type": l.type, "mixer": l.mixer.to_dict(),
+                          "mlp": None if l.ff is None else {"ff": l.ff, "kind": "dense"}} for l in self.layers]
+        if self.eos_token_id:
+            out["eos_token_id"] = list(self.eos_token_id)
+        return out
+
+
 def read_config_json(model_dir: str | Path) -> dict:
     path = Path(model_dir) / "config.json"
     if not path.is_file():

@@ -1,8 +1,8 @@
 // Decode attention over the paged cache (bfloat16): split-K flash decoding, one CTA per
 // (token, kv head, split), all query heads of the kv head's group share every K/V tile.
 //
-// For the token at position p of its request the CTA reads keys lo..p
-// (lo = window ? max(0, p - window + 1) : 0) of its split, 64 keys a chunk, in a three-stage
+// For the token at position p of its request the CTA reads keys lo..p (lo by the mask's rule, the
+// kept first keys in front of them: attention_mask.cuh) of its split, 64 keys a chunk, in a three-stage
 // cp.async pipeline through the block table.  The group's query heads (rep = nq / nkv <= 16) are
 // the 16 rows of an m16n8k16 tensor-core tile: S = Q K^T, online softmax in float32 (base 2),
 // O += P V.  Each of the 4 warps takes 16 keys of a chunk and keeps its own running
@@ -34,7 +34,8 @@ struct DecodeParams {
     const int* token_list;    // tokens handled (nullptr: 0 .. n-1)
     float* part_o;            // [n, nq, splits, D]  (splits > 1)
     float* part_lse;          // [n, nq, splits]
-    int table_stride, nq, nkv, logP, window, num_splits;
+    int table_stride, nq, nkv, logP, num_splits;
+    AttnMask mask;           // attention_mask.cuh: window, blocks of positions, kept first keys
     float scale_log2;         // softmax scale * log2(e)
 };
 
@@ -51,12 +52,12 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const Dec
     const int t = p.token_list ? p.token_list[ti] : ti;
     const int r = p.token_row[t], pos = p.positions[t];
     const int rep = p.nq / p.nkv;
-    const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int lo = mask_lo(p.mask, pos), vlo = mask_vlo(p.mask, lo);   // virtual indices vlo..pos: kept keys, then lo..pos
     const int hi = pos + 1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, tq = lane & 3;
 
-    const int n_chunks = (hi - lo + DEC_CHUNK - 1) / DEC_CHUNK;
+    const int n_chunks = (hi - vlo + DEC_CHUNK - 1) / DEC_CHUNK;
     const int per = (n_chunks + p.num_splits - 1) / p.num_splits;
     const int c0 = split * per, c1 = min(n_chunks, c0 + per);
     if (c0 >= c1) {      // an empty split: weight zero in the merge
@@ -88,7 +89,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const Dec
     auto load_chunk = [&](int c, int stage) {
         if (c < c1)
             load_kv_pair_rows<D, LDS, DEC_THREADS>(sK + stage * DEC_CHUNK * LDS, sV + stage * DEC_CHUNK * LDS,
-                                                   p.k_pages, p.v_pages, table, lo + c * DEC_CHUNK, DEC_CHUNK, lo, hi,
+                                                   p.k_pages, p.v_pages, table, vlo + c * DEC_CHUNK, DEC_CHUNK, vlo, lo, hi,
                                                    p.logP, p.nkv, kvh);
         cp_async_commit();      // a group per chunk slot, empty past the end, keeps the wait count fixed
     };
@@ -102,7 +103,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const Dec
         load_chunk(c + DEC_STAGES - 1, (c - c0 + DEC_STAGES - 1) % DEC_STAGES);
         cp_async_wait<DEC_STAGES - 1>();
         __syncthreads();
-        const int wkey0 = lo + c * DEC_CHUNK + warp * 16;     // first key of this warp's 16
+        const int wkey0 = vlo + c * DEC_CHUNK + warp * 16;    // first (virtual) key of this warp's 16
         if (wkey0 < hi) {
             const bf16* kbase = sK + (stage * DEC_CHUNK + warp * 16) * LDS;
             const bf16* vbase = sV + (stage * DEC_CHUNK + warp * 16) * LDS;
@@ -273,7 +274,7 @@ extern "C" int acorn_attention_decode(const void* q, int64_t q_stride, void* out
                                       int table_stride, const int* token_row, const int* positions,
                                       const int* token_list, int n, int nq, int nkv, int d, int P, float scale,
                                       int window, int num_splits, float* part_o, float* part_lse,
-                                      cudaStream_t stream) {
+                                      int chunk, int keep, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (!acorn_attention_decode_supported(nq, nkv, d) || num_splits < 1 || num_splits > DEC_MAX_SPLITS || n > 65535)
         return ACORN_ERR_UNSUPPORTED;
@@ -285,7 +286,7 @@ extern "C" int acorn_attention_decode(const void* q, int64_t q_stride, void* out
     p.token_list = token_list; p.part_o = part_o; p.part_lse = part_lse;
     p.table_stride = table_stride; p.nq = nq; p.nkv = nkv; p.logP = acorn_log2_exact(P);
     if (p.logP < 0) return ACORN_ERR_UNSUPPORTED;   // page sizes are powers of two
-    p.window = window; p.num_splits = num_splits;
+    p.mask = AttnMask{window, chunk, keep}; p.num_splits = num_splits;
     p.scale_log2 = scale * 1.4426950408889634f;
     int rc;
     switch (d) {

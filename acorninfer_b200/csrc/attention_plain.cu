@@ -4,7 +4,8 @@
 //
 // One block per (token, kv head, up to eight of that kv head's query heads): the query heads of a
 // group read the same keys and values, so a key row is fetched once for all of them.  The query at
-// absolute position p of row r reads keys lo..p, lo = window ? max(0, p - window + 1) : 0, from
+// absolute position p of row r reads keys lo..p (lo by the mask's rule, and the kept first keys:
+// attention_mask.cuh), from
 // the pages of its row: key j lives in page block_table[r * stride + j / P - page_base[r]], slot
 // j % P, cache layout [num_pages, nkv, P, d].  Query head h uses kv head h / (nq / nkv).
 // Scores, softmax (online, per chunk of keys) and the weighted sum are float32.
@@ -18,6 +19,7 @@
 // that the loads from the pages are 64 contiguous bytes to four lanes).  Weighted sum: 128 threads across the head's dimensions times four
 // groups that take every fourth key; the groups' sums are added at the end.
 #include "common.cuh"
+#include "attention_mask.cuh"
 
 #define PLAIN_THREADS 512
 #define PLAIN_LANES 128                 // threads across the dimensions of a head
@@ -31,14 +33,14 @@ __global__ void __launch_bounds__(PLAIN_THREADS) attention_plain_kernel(
     const T* __restrict__ q, int64_t q_stride, T* __restrict__ out, const T* __restrict__ k_pages,
     const T* __restrict__ v_pages, const int* __restrict__ block_table, const int* __restrict__ page_base,
     int table_stride, const int* __restrict__ token_row, const int* __restrict__ positions, int nq, int nkv, int d,
-    int P, float scale, int window, int parts, int dv, const float* __restrict__ sink, int hpb) {
+    int P, float scale, AttnMask mask, int parts, int dv, int v_row, const float* __restrict__ sink, int hpb) {
     extern __shared__ __align__(16) float smem[];
     float* qs = smem;                                   // [heads][d], scaled
     float* sc = smem + PLAIN_HEADS * d;                 // [heads][PLAIN_THREADS] probabilities of the chunk
     uint4* stage = reinterpret_cast<uint4*>(sc + PLAIN_HEADS * PLAIN_THREADS);   // [warps][32][5] pieces of key rows
     // rows of the pages start on 16-byte boundaries: they can be fetched 16 bytes at a time
     const bool rows_aligned = (d * sizeof(T)) % 16 == 0 && (reinterpret_cast<uintptr_t>(k_pages) & 15) == 0;
-    __shared__ int64_t row_at[PLAIN_THREADS];           // where each key of the chunk starts in the pages (keys and values alike)
+    __shared__ int64_t row_at[PLAIN_THREADS];           // the row of each key of the chunk in the pages (keys and values alike)
     __shared__ float red_max[PLAIN_HEADS][PLAIN_WARPS];
     __shared__ float red_sum[PLAIN_HEADS][PLAIN_WARPS];
 
@@ -48,7 +50,7 @@ __global__ void __launch_bounds__(PLAIN_THREADS) attention_plain_kernel(
     const int h0 = kvh * rep + part * hpb;                 // hpb <= PLAIN_HEADS query heads a block
     const int G = min(hpb, rep - part * hpb);
     const int r = token_row[t], pos = positions[t];
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int lo = mask_lo(mask, pos), vlo = mask_vlo(mask, lo);     // virtual indices vlo..pos: kept keys, then lo..pos
     const int* table = block_table + (int64_t)r * table_stride - page_base[r];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int i = threadIdx.x; i < G * d; i += PLAIN_THREADS)
@@ -67,14 +69,17 @@ __global__ void __launch_bounds__(PLAIN_THREADS) attention_plain_kernel(
     }
     __syncthreads();
 
-    for (int base = lo; base <= pos; base += PLAIN_THREADS) {
-        const int j = base + threadIdx.x;
+    for (int base = vlo; base <= pos; base += PLAIN_THREADS) {
+        const int j = base + threadIdx.x;                 // virtual index; key mask_key(j, vlo, lo)
         float s[PLAIN_HEADS];
 #pragma unroll
         for (int g = 0; g < PLAIN_HEADS; ++g) s[g] = -INFINITY;
         const bool live = j <= pos;
         int64_t at = 0;
-        if (live) at = (((int64_t)table[j / P] * nkv + kvh) * P + (j % P)) * d;
+        if (live) {
+            const int key = mask_key(j, vlo, lo);
+            at = ((int64_t)table[key / P] * nkv + kvh) * P + (key % P);
+        }
         row_at[threadIdx.x] = at;
         __syncwarp();
         const int wbase = warp * 32;
@@ -98,7 +103,7 @@ __global__ void __launch_bounds__(PLAIN_THREADS) attention_plain_kernel(
                         const int key = c * 8 + (lane >> 2);
                         piece[c] = make_uint4(0u, 0u, 0u, 0u);
                         if (key < nlive)
-                            piece[c] = *reinterpret_cast<const uint4*>(k_pages + row_at[wbase + key] + i + (lane & 3) * EPC);
+                            piece[c] = *reinterpret_cast<const uint4*>(k_pages + row_at[wbase + key] * d + i + (lane & 3) * EPC);
                     }
 #pragma unroll
                     for (int c = 0; c < 4; ++c) mine[(c * 8 + (lane >> 2)) * 5 + (lane & 3)] = piece[c];
@@ -124,7 +129,7 @@ __global__ void __launch_bounds__(PLAIN_THREADS) attention_plain_kernel(
                 }
             }
             if (live) {
-                const T* kp = k_pages + at;
+                const T* kp = k_pages + at * d;
                 for (; i < d; ++i) {
                     const float kv = to_float(kp[i]);
 #pragma unroll
@@ -186,7 +191,7 @@ __global__ void __launch_bounds__(PLAIN_THREADS) attention_plain_kernel(
                     const int jj = j0 + u * PLAIN_KGROUPS;
                     v[u] = 0.f;
                     if (jj < n && dim < dv)
-                        v[u] = to_float(v_pages[row_at[jj] + dim]);
+                        v[u] = to_float(v_pages[row_at[jj] * v_row + dim]);
                 }
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
@@ -233,9 +238,11 @@ extern "C" int acorn_attention_plain(const void* q, int64_t q_stride, void* out,
                                      const void* v_pages, const int* block_table, const int* page_base,
                                      int table_stride, const int* token_row, const int* positions,
                                      int tokens, int nq, int nkv, int d, int P, float scale, int window,
-                                     int dtype, int dv, const float* sink, cudaStream_t stream) {
+                                     int dtype, int dv, const float* sink, int chunk, int keep, int v_row,
+                                     cudaStream_t stream) {
     if (tokens <= 0) return 0;
-    if (dv < 1 || dv > d) return ACORN_ERR_UNSUPPORTED;
+    if (dv < 1 || dv > PLAIN_MAX_D || v_row < dv) return ACORN_ERR_UNSUPPORTED;
+    const AttnMask mask = {window, chunk, keep};
     if (d < 1 || d > PLAIN_MAX_D || nkv < 1 || nq % nkv != 0) return ACORN_ERR_UNSUPPORTED;
     // Eight query heads of a kv head share a block (a key row is fetched once for all of them) unless that
     // leaves most of the device idle (few tokens, few kv heads): then fewer heads a block.  A head's
@@ -257,6 +264,6 @@ extern "C" int acorn_attention_plain(const void* q, int64_t q_stride, void* out,
     dim3 grid(tokens, nkv * parts);
     ACORN_DISPATCH_DTYPE(dtype, T, (attention_plain_kernel<T><<<grid, PLAIN_THREADS, smem, stream>>>(
         (const T*)q, q_stride, (T*)out, (const T*)k_pages, (const T*)v_pages, block_table, page_base,
-        table_stride, token_row, positions, nq, nkv, d, P, scale, window, parts, dv, sink, hpb)));
+        table_stride, token_row, positions, nq, nkv, d, P, scale, mask, parts, dv, v_row, sink, hpb)));
     return acorn_launch_status();
 }

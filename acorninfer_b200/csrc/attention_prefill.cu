@@ -6,7 +6,8 @@
 // lists them: tile -> row, first token).  One CTA handles one tile for one query head: its
 // 4 warps hold 16 queries each as the rows of m16n8k16 tensor-core tiles and walk the keys
 // lo..last query's position in chunks of 64, double-buffered with cp.async.  Per chunk
-// S = Q K^T, causal (and window) mask by absolute positions, online softmax in float32
+// S = Q K^T, causal mask by absolute positions (with a window, blocks of positions or kept first
+// keys: attention_mask.cuh; the keys are walked as virtual indices), online softmax in float32
 // (base 2), O += P V.  A tile may hold a single token (a decoded token in a mixed step).
 //
 // Reference: the reference gathers each request's K/V into a dense tensor per layer and
@@ -29,7 +30,8 @@ struct PrefillParams {
     const int* row_start;     // [rows + 1] offsets of the rows in the token arrays
     const int* row_pos;       // [rows] tokens of the request in the cache before the step
     const int* tiles;         // [n_tiles, 2]: row, first token of the tile relative to the row
-    int table_stride, nq, nkv, logP, window;
+    int table_stride, nq, nkv, logP;
+    AttnMask mask;
     float scale_log2;
 };
 
@@ -49,8 +51,9 @@ __global__ void __launch_bounds__(PRE_THREADS) attention_prefill_kernel(const Pr
     const int kvh = head / (p.nq / p.nkv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, tq = lane & 3;
-    const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
-    const int hi = pos0 + n_q;                               // keys lo .. hi-1 are read by the tile
+    const int lo = mask_lo(p.mask, pos0);                    // the first query's rule starts here; later queries' no earlier
+    const int vlo = mask_vlo(p.mask, lo);                    // kept first keys ride in front: virtual indices vlo .. hi-1
+    const int hi = pos0 + n_q;
     const int* table = p.block_table + (int64_t)r * p.table_stride - p.page_base[r];
 
     // this warp's queries: rows g and g+8 of its 16
@@ -72,14 +75,14 @@ __global__ void __launch_bounds__(PRE_THREADS) attention_prefill_kernel(const Pr
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     const int qpos[2] = {pos0 + qi0, pos0 + qi1};
     const int warp_last_pos = pos0 + min(warp * 16 + 15, n_q - 1);     // last position this warp's queries reach
-    const int warp_first_lo = p.window > 0 ? max(0, pos0 + warp * 16 - p.window + 1) : 0;
+    const int warp_first_lo = mask_lo(p.mask, pos0 + warp * 16);
     const bool warp_active = warp * 16 < n_q;
 
-    const int n_chunks = (hi - lo + PRE_BN - 1) / PRE_BN;
+    const int n_chunks = (hi - vlo + PRE_BN - 1) / PRE_BN;
     auto load_chunk = [&](int c, int stage) {
-        const int key0 = lo + c * PRE_BN;
+        const int key0 = vlo + c * PRE_BN;
         load_kv_pair_rows<D, LDS, PRE_THREADS>(sK + stage * PRE_BN * LDS, sV + stage * PRE_BN * LDS, p.k_pages,
-                                               p.v_pages, table, key0, PRE_BN, lo, hi, p.logP, p.nkv, kvh);
+                                               p.v_pages, table, key0, PRE_BN, vlo, lo, hi, p.logP, p.nkv, kvh);
         cp_async_commit();
     };
 
@@ -93,9 +96,9 @@ __global__ void __launch_bounds__(PRE_THREADS) attention_prefill_kernel(const Pr
             cp_async_wait<0>();
         }
         __syncthreads();
-        const int key0 = lo + c * PRE_BN;
-        // skip chunks that no query of this warp may see
-        if (warp_active && key0 <= warp_last_pos && key0 + PRE_BN > warp_first_lo) {
+        const int key0 = vlo + c * PRE_BN;
+        // skip chunks that no query of this warp may see (kept first keys, virtual indices below lo, all see)
+        if (warp_active && key0 <= warp_last_pos && (key0 + PRE_BN > warp_first_lo || key0 < lo)) {
             const bf16* kbase = sK + stage * PRE_BN * LDS;
             const bf16* vbase = sV + stage * PRE_BN * LDS;
             float s[PRE_BN / 8][4];
@@ -117,9 +120,9 @@ __global__ void __launch_bounds__(PRE_THREADS) attention_prefill_kernel(const Pr
             for (int j = 0; j < PRE_BN / 8; ++j)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const int key = key0 + j * 8 + 2 * tq + (e & 1);
+                    const int v = key0 + j * 8 + 2 * tq + (e & 1);
                     const int qp = qpos[e >> 1];
-                    const bool ok = key <= qp && key < hi && (p.window <= 0 || key > qp - p.window);
+                    const bool ok = v < hi && mask_sees(p.mask, qp, mask_key(v, vlo, lo));
                     s[j][e] = ok ? s[j][e] * p.scale_log2 : -INFINITY;
                     mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
                 }
@@ -203,7 +206,7 @@ extern "C" int acorn_attention_prefill(const void* q, int64_t q_stride, void* ou
                                        const void* v_pages, const int* block_table, const int* page_base,
                                        int table_stride, const int* row_start, const int* row_pos,
                                        const int* tiles, int n_tiles, int nq, int nkv, int d, int P, float scale,
-                                       int window, cudaStream_t stream) {
+                                       int window, int chunk, int keep, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (!acorn_attention_prefill_supported(nq, nkv, d)) return ACORN_ERR_UNSUPPORTED;
     PrefillParams p;
@@ -212,7 +215,7 @@ extern "C" int acorn_attention_prefill(const void* q, int64_t q_stride, void* ou
     p.block_table = block_table; p.page_base = page_base; p.row_start = row_start; p.row_pos = row_pos;
     p.tiles = tiles; p.table_stride = table_stride; p.nq = nq; p.nkv = nkv; p.logP = acorn_log2_exact(P);
     if (p.logP < 0) return ACORN_ERR_UNSUPPORTED;   // page sizes are powers of two
-    p.window = window;
+    p.mask = AttnMask{window, chunk, keep};
     p.scale_log2 = scale * 1.4426950408889634f;
     switch (d) {
         case 16: return launch_prefill<16>(p, n_tiles, stream);

@@ -2,22 +2,22 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------- embedding
-// out32[t, :] = table[ids[t], :]   (float32 residual stream)
+// out32[t, :] = table[ids[t], :] * scale   (float32 residual stream)
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                             float* __restrict__ out32, int H) {
+                             float* __restrict__ out32, int H, float scale) {
     pdl_wait();
     pdl_trigger();
     const int t = blockIdx.x;
     const T* row = table + (int64_t)ids[t] * H;
     float* o = out32 + (int64_t)t * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_float(row[i]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_float(row[i]) * scale;
 }
 
 extern "C" int acorn_embed(const int* ids, const void* table, float* out32, int tokens, int H,
-                           int dtype, cudaStream_t stream) {
+                           int dtype, float scale, cudaStream_t stream) {
     if (tokens <= 0) return 0;
-    ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(embed_kernel<T>, dim3(tokens), dim3(256), 0, stream, ids, (const T*)table, out32, H));
+    ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(embed_kernel<T>, dim3(tokens), dim3(256), 0, stream, ids, (const T*)table, out32, H, scale));
     return ACORN_ERR_UNSUPPORTED;
 }
 
@@ -137,12 +137,24 @@ extern "C" int acorn_add_rmsnorm(float* resid32, const void* delta, const float*
     return ACORN_ERR_UNSUPPORTED;
 }
 
-// ---------------------------------------------------------------- SwiGLU
-// out[t, i] = silu(gate) * up,   silu(z) = z / (1 + exp(-z)).  A row of gu holds, per block of b
+// ---------------------------------------------------------------- gated linear unit (SwiGLU, GeGLU)
+// out[t, i] = act(gate) * up;  act 0: silu(z) = z / (1 + exp(-z)),  act 1: the tanh form of gelu,
+// 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))) = z sigmoid(2 sqrt(2/pi) (z + 0.044715 z^3)).  A row of gu holds, per block of b
 // outputs, b gate values then b up values: gate of output i at (i / b) * 2b + i % b, up b further.
 // b = I is the plain layout [gate | up].
+__device__ __forceinline__ float glu_act(float g, int act) {
+    if (act == 1) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    return g / (1.f + expf(-g));
+}
+
+// the same by the fast float32 instructions (relative error about 2^-22), for results rounded to bfloat16
+template <int ACT> __device__ __forceinline__ float glu_act_fast(float g) {
+    const float z = ACT == 1 ? 1.5957691216057308f * (g + 0.044715f * g * g * g) : g;
+    return __fdividef(g, 1.f + __expf(-z));
+}
+
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t total, int I, int b) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t total, int I, int b, int act) {
     pdl_wait();
     pdl_trigger();
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -152,13 +164,14 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
         const int64_t gi = t * 2 * I + (int64_t)(i / b) * 2 * b + i % b;
         const float g = to_float(gu[gi]);
         const float u = to_float(gu[gi + b]);
-        out[idx] = from_float<T>(g / (1.f + expf(-g)) * u);
+        out[idx] = from_float<T>(glu_act(g, act) * u);
     }
 }
 
 // bfloat16 rows whose block width b is a multiple of 8: 16-byte loads and stores (b8 = b / 8).
 // blockIdx.y is the token, so that no index is divided by the row width; a thread takes two
 // 16-byte chunks of outputs a step (four loads in flight).
+template <int ACT>
 __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int I8, int b8) {
     pdl_wait();
     pdl_trigger();
@@ -173,8 +186,7 @@ __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restri
             const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw[k]));
             // exp and the quotient by the fast float32 instructions (relative error about 2^-22, far below
             // the bfloat16 rounding of the result): with the exact ones the kernel is bound by arithmetic
-            __nv_bfloat162 o = __floats2bfloat162_rn(__fdividef(g.x, 1.f + __expf(-g.x)) * u.x,
-                                                     __fdividef(g.y, 1.f + __expf(-g.y)) * u.y);
+            __nv_bfloat162 o = __floats2bfloat162_rn(glu_act_fast<ACT>(g.x) * u.x, glu_act_fast<ACT>(g.y) * u.y);
             ow[k] = *reinterpret_cast<uint32_t*>(&o);
         }
         return make_uint4(ow[0], ow[1], ow[2], ow[3]);
@@ -195,22 +207,25 @@ __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restri
     }
 }
 
-extern "C" int acorn_swiglu(const void* gu, void* out, int tokens, int I, int block, int dtype,
+extern "C" int acorn_swiglu(const void* gu, void* out, int tokens, int I, int block, int dtype, int act,
                             cudaStream_t stream) {
     const int64_t total = (int64_t)tokens * I;
     if (total <= 0) return 0;
-    if (block <= 0 || I % block != 0) return ACORN_ERR_UNSUPPORTED;
+    if (block <= 0 || I % block != 0 || act < 0 || act > 1) return ACORN_ERR_UNSUPPORTED;
     if (dtype == ACORN_DTYPE_BF16 && block % 8 == 0 && tokens <= 65535) {
         const int I8 = I / 8;
         int bx = (I8 + 511) / 512;                  // 256 threads, two chunks each
         if (bx < 1) bx = 1;
-        return acorn_launch(swiglu_bf16x8_kernel, dim3(bx, tokens), dim3(256), 0, stream, (const bf16*)gu, (bf16*)out,
+        if (act == 1)
+            return acorn_launch(swiglu_bf16x8_kernel<1>, dim3(bx, tokens), dim3(256), 0, stream, (const bf16*)gu,
+                                (bf16*)out, I8, block / 8);
+        return acorn_launch(swiglu_bf16x8_kernel<0>, dim3(bx, tokens), dim3(256), 0, stream, (const bf16*)gu, (bf16*)out,
                             I8, block / 8);
     }
     int64_t blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(swiglu_kernel<T>, dim3((int)blocks), dim3(256), 0, stream,
-                                                       (const T*)gu, (T*)out, total, I, block));
+                                                       (const T*)gu, (T*)out, total, I, block, act));
     return ACORN_ERR_UNSUPPORTED;
 }
 
@@ -314,5 +329,106 @@ extern "C" int acorn_rmsnorm_add(float* resid32, const void* y, const float* w, 
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(rmsnorm_add_kernel<T>, dim3(rows), dim3(threads), 0, stream, resid32,
                                                        (const T*)y, w, (T*)rounded, H, eps));
+    return ACORN_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------- add + LayerNorm (weight and bias)
+// v = resid32[row] (+ delta[row]) (+ delta2[row]);  if write_resid: resid32[row] = v
+// out[r] = (v - mean(v)) * rsqrt(mean((v - mean(v))^2) + eps) * w + b      (float32, one rounding)
+// row = row_idx ? row_idx[r] : r; with row_idx the residual is not written back.  Two deltas: the two
+// sublayers of a block whose mixer and feed-forward read the same normed rows.  The row is kept in
+// shared memory between the passes; the variance is taken of the deviations (two passes), not as
+// mean(v^2) - mean(v)^2.
+template <typename T>
+__global__ void add_layernorm_kernel(float* __restrict__ resid32, const T* __restrict__ delta,
+                                     const T* __restrict__ delta2, const float* __restrict__ w,
+                                     const float* __restrict__ b, T* __restrict__ out,
+                                     const int* __restrict__ row_idx, int H, float eps) {
+    extern __shared__ float rowv[];
+    __shared__ float scratch[32];
+    pdl_wait();
+    pdl_trigger();
+    const int r = blockIdx.x;
+    const int64_t row = row_idx ? row_idx[r] : r;
+    const bool write_resid = (row_idx == nullptr) && (delta != nullptr || delta2 != nullptr);
+    float* x = resid32 + row * H;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = x[i];
+        if (delta) v += to_float(delta[row * H + i]);
+        if (delta2) v += to_float(delta2[row * H + i]);
+        if (write_resid) x[i] = v;
+        rowv[i] = v;
+        s += v;
+    }
+    const float mean = block_sum(s, scratch) / (float)H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float dv = rowv[i] - mean;
+        ss += dv * dv;
+    }
+    const float inv = rsqrtf(block_sum(ss, scratch) / (float)H + eps);
+    T* o = out + (int64_t)r * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+        o[i] = from_float<T>((rowv[i] - mean) * inv * w[i] + (b ? b[i] : 0.f));
+}
+
+extern "C" int acorn_add_layernorm(float* resid32, const void* delta, const void* delta2, const float* w,
+                                   const float* b, void* out, const int* row_idx, int rows, int H, float eps,
+                                   int dtype, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if ((size_t)H * sizeof(float) > 48 * 1024) return ACORN_ERR_UNSUPPORTED;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(add_layernorm_kernel<T>, dim3(rows), dim3(threads),
+                                                       (size_t)H * sizeof(float), stream, resid32, (const T*)delta,
+                                                       (const T*)delta2, w, b, (T*)out, row_idx, H, eps));
+    return ACORN_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------- resid32 += delta
+template <typename T>
+__global__ void add_into_kernel(float* __restrict__ resid32, const T* __restrict__ delta, int64_t n) {
+    pdl_wait();
+    pdl_trigger();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        resid32[i] += to_float(delta[i]);
+}
+
+extern "C" int acorn_add_into(float* resid32, const void* delta, int64_t n, int dtype, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    int64_t blocks = (n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(add_into_kernel<T>, dim3((int)blocks), dim3(256), 0, stream,
+                                                       resid32, (const T*)delta, n));
+    return ACORN_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------- a gate per head
+// out[t, h, :] = x[t, h, :] * scale * sigmoid(g[t * ldg + h]): every head's output times one number of its
+// own, a function of the layer's input (g is a slice of a wider product; null: times scale); float32, one
+// rounding.  out may be x itself, or rows of another buffer (row stride ldo).
+template <typename T>
+__global__ void head_gate_kernel(const T* x, const T* __restrict__ g, int64_t ldg, T* out, int64_t ldo, int heads,
+                                 int d, int64_t total, float scale) {
+    pdl_wait();
+    pdl_trigger();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t th = i / d;
+        const int64_t t = th / heads;
+        const int h = (int)(th - t * heads);
+        const float f = g ? scale / (1.f + expf(-to_float(g[t * ldg + h]))) : scale;
+        out[t * ldo + (i - t * heads * d)] = from_float<T>(to_float(x[i]) * f);
+    }
+}
+
+extern "C" int acorn_head_gate(const void* x, const void* g, int64_t ldg, void* out, int64_t ldo, int tokens, int heads,
+                               int d, float scale, int dtype, cudaStream_t stream) {
+    const int64_t total = (int64_t)tokens * heads * d;
+    if (total <= 0) return 0;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(head_gate_kernel<T>, dim3((int)blocks), dim3(256), 0, stream,
+                                                       (const T*)x, (const T*)g, ldg, (T*)out, ldo, heads, d, total,
+                                                       scale));
     return ACORN_ERR_UNSUPPORTED;
 }

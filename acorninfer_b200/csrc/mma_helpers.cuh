@@ -9,6 +9,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "attention_mask.cuh"
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -85,19 +86,23 @@ __device__ __forceinline__ void load_kv_rows(bf16* sdst, const bf16* __restrict_
 }
 
 // The same for K and V together: a key's row has the same offset in both page tensors, so the
-// block-table lookup and the address arithmetic are done once for the pair.
+// block-table lookup and the address arithmetic are done once for the pair.  The rows are *virtual*
+// key indices (see attention_mask.cuh): index v in [vlo, hi) stands for key v - vlo below lo (a
+// kept first key) and for key v from lo on; with vlo == lo they are the keys themselves.
 template <int D, int LDS, int THREADS>
 __device__ __forceinline__ void load_kv_pair_rows(bf16* sk, bf16* sv, const bf16* __restrict__ k_pages,
                                                   const bf16* __restrict__ v_pages, const int* __restrict__ table,
-                                                  int key0, int rows, int lo, int hi, int logP, int nkv, int kvh) {
+                                                  int key0, int rows, int vlo, int lo, int hi, int logP, int nkv,
+                                                  int kvh) {
     constexpr int SEGS = D / 8;
     const int pmask = (1 << logP) - 1;
     for (int idx = threadIdx.x; idx < rows * SEGS; idx += THREADS) {
         const int row = idx / SEGS, seg = idx - row * SEGS;
-        const int key = key0 + row;
-        const bool valid = key >= lo && key < hi;
+        const int v = key0 + row;
+        const bool valid = v >= vlo && v < hi;
         int64_t off = 0;
         if (valid) {
+            const int key = mask_key(v, vlo, lo);
             const int page = __ldg(table + (key >> logP));
             off = ((((int64_t)page * nkv + kvh) << logP) + (key & pmask)) * D + seg * 8;
         }

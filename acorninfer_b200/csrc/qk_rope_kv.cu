@@ -11,7 +11,9 @@
 // Cache layout per layer: [num_pages, nkv, page_size, d]; the token at position p of
 // row r lives in page block_table[r * table_stride + p / P - page_base[r]], slot p % P.
 // With write_kv = 0 only the query heads are processed (a layer that reads another
-// layer's cache).
+// layer's cache).  Value heads may have a width of their own (dv; their pages then hold rows of dv),
+// a row of qkv may be wider than its heads (ld elements), and with v_from_k the values are the keys as
+// projected, before norm and rotation: the row then holds no value heads, [q | k] only.
 #include "common.cuh"
 
 template <typename T>
@@ -21,7 +23,7 @@ __global__ void qk_rope_kv_kernel(T* __restrict__ qkv, const float* __restrict__
                                   const int* __restrict__ block_table, const int* __restrict__ page_base,
                                   int table_stride, T* __restrict__ k_pages, T* __restrict__ v_pages,
                                   int tokens, int nq, int nkv, int d, int rot, int pairing, int P,
-                                  float eps, int write_kv) {
+                                  float eps, int write_kv, int64_t ld, int dv, int v_from_k) {
     extern __shared__ float smem[];
     pdl_wait();
     pdl_trigger();
@@ -33,7 +35,7 @@ __global__ void qk_rope_kv_kernel(T* __restrict__ qkv, const float* __restrict__
     const int t = (int)(item / heads);
     const int h = (int)(item - (int64_t)t * heads);
     float* x = smem + warp * d;
-    T* src = qkv + ((int64_t)t * (nq + 2 * nkv) + h) * d;
+    T* src = qkv + (int64_t)t * ld + (int64_t)h * d;
     const int pos = positions[t];
 
     T* dst = src;   // q: in place
@@ -41,11 +43,13 @@ __global__ void qk_rope_kv_kernel(T* __restrict__ qkv, const float* __restrict__
         const int r = token_row[t];
         const int kvh = (h - nq) % nkv;
         const int page = block_table[(int64_t)r * table_stride + (pos / P - page_base[r])];
-        T* base = (h < nq + nkv) ? k_pages : v_pages;
-        dst = base + (((int64_t)page * nkv + kvh) * P + (pos % P)) * d;
+        const int64_t slot = ((int64_t)page * nkv + kvh) * P + (pos % P);
+        dst = (h < nq + nkv) ? k_pages + slot * d : v_pages + slot * dv;
+        if (h >= nq + nkv)      // the value head's source: its own columns, or the key head as projected
+            src = qkv + (int64_t)t * ld + (v_from_k ? (int64_t)(nq + kvh) * d : (int64_t)(nq + nkv) * d + (int64_t)kvh * dv);
     }
     if (h >= nq + nkv) {   // value head: copy
-        for (int i = lane; i < d; i += 32) dst[i] = src[i];
+        for (int i = lane; i < dv; i += 32) dst[i] = src[i];
         return;
     }
     float ss = 0.f;
@@ -187,10 +191,12 @@ extern "C" int acorn_qk_rope_kv(void* qkv, const float* q_w, const float* k_w, c
                                 const int* positions, const int* token_row, const int* block_table,
                                 const int* page_base, int table_stride, void* k_pages, void* v_pages,
                                 int tokens, int nq, int nkv, int d, int rot, int pairing, int P,
-                                float eps, int write_kv, int dtype, cudaStream_t stream) {
+                                float eps, int write_kv, int dtype, int64_t ld, int dv, int v_from_k,
+                                cudaStream_t stream) {
     if (tokens <= 0) return 0;
-    if (d > 1024 || rot > d || (rot & 1)) return ACORN_ERR_UNSUPPORTED;
-    if (rot == d && pairing == 0 && (d == 16 || d == 32 || d == 64 || d == 128 || d == 256)) {
+    if (d > 1024 || rot > d || (rot & 1) || dv < 1 || dv > 1024 || (v_from_k && dv != d)) return ACORN_ERR_UNSUPPORTED;
+    if (rot == d && pairing == 0 && dv == d && !v_from_k && ld == (int64_t)(nq + 2 * nkv) * d &&
+        (d == 16 || d == 32 || d == 64 || d == 128 || d == 256)) {
 #define ROPE_VEC(G)                                                                                                  \
     ACORN_DISPATCH_DTYPE(dtype, T, return (launch_rope_vec<T, G>((T*)qkv, q_w, k_w, inv_freq, positions, token_row,   \
                                                                   block_table, page_base, table_stride, (T*)k_pages,   \
@@ -213,7 +219,7 @@ extern "C" int acorn_qk_rope_kv(void* qkv, const float* q_w, const float* k_w, c
     ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(
         qk_rope_kv_kernel<T>, dim3((unsigned)blocks), dim3(warps * 32), smem, stream, (T*)qkv, q_w, k_w, inv_freq,
         positions, token_row, block_table, page_base, table_stride, (T*)k_pages, (T*)v_pages, tokens, nq, nkv, d, rot,
-        pairing, P, eps, write_kv));
+        pairing, P, eps, write_kv, ld, dv, v_from_k));
     return ACORN_ERR_UNSUPPORTED;
 }
 

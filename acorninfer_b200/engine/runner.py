@@ -68,7 +68,7 @@ class ModelRunner:
         # Padding a prompt portion writes keys and values for tokens that do not exist: harmless where a
         # request's next tokens overwrite them before they are read, which holds for caches that keep every
         # key; not for windows (pages are given back by position) nor for state that every token updates.
-        self.prefill_graph = not self.manager.state_needs and all(g.window is None for g in self.manager.groups)
+        self.prefill_graph = not self.manager.state_needs and all(g.window is None and g.needs.chunk is None for g in self.manager.groups)
         self._graphs: OrderedDict[tuple, object] = OrderedDict()        # least recently replayed first
         self._graph_seen: OrderedDict[tuple, int] = OrderedDict()
         self._graph_pool = None

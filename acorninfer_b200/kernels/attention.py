@@ -113,19 +113,30 @@ def _merge_free(nq: int, nkv: int, d: int, P: int) -> int:
     return _MERGE_FREE[key]
 
 
+def _key_bound(table_keys: int, window: int | None, chunk: int | None, keep_first: int) -> int:
+    """A bound on the keys any query of the step reads, from the table's width and the mask."""
+    spans = [s for s in (window, chunk) if s]
+    return min(table_keys, min(spans) + keep_first) if spans else table_keys
+
+
 def paged_attention(qkv: torch.Tensor, inputs, group, cache, nq: int, nkv: int, d: int, scale: float,
-                    window: int | None) -> torch.Tensor:
-    """Attention of all tokens of the step; q is the head of ``qkv`` ([T, (nq + 2 nkv) d])."""
+                    window: int | None, chunk: int | None = None, keep_first: int = 0,
+                    value_dim: int | None = None) -> torch.Tensor:
+    """Attention of all tokens of the step; q is the head of ``qkv`` ([T, >= nq d]).  ``window``, ``chunk``,
+    ``keep_first``: which earlier keys a query reads (see ``parts/attention.py``); ``value_dim``: width of the
+    value rows where it is not ``d``.  The tensor-core kernels take values as wide as keys; the TMA and
+    tcgen05 kernels know windows only."""
     P = cache.k_pages.shape[2]
-    if qkv.dtype == torch.bfloat16:
+    windowed_only = not chunk and not keep_first
+    mask = {"chunk": chunk, "keep_first": keep_first}
+    if qkv.dtype == torch.bfloat16 and (value_dim is None or value_dim == d):
         if inputs.plan.all_decode and ops.attention_decode_supported(nq, nkv, d) and inputs.num_tokens <= 65535:
-            bound = group.block_table.shape[1] * P
-            if window:
-                bound = min(bound, window)
-            splits = decode_splits(inputs.num_rows, nkv, bound, d, sm_count(qkv.device), _merge_free(nq, nkv, d, P))
+            bound = _key_bound(group.block_table.shape[1] * P, window, chunk, keep_first)
+            splits = decode_splits(inputs.num_rows, nkv, bound, d, sm_count(qkv.device),
+                                   _merge_free(nq, nkv, d, P) if windowed_only else 1)
             return ops.attention_decode(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,
                                         group.page_base, inputs.token_row, inputs.positions, inputs.num_tokens,
-                                        nq, nkv, d, scale, window, splits)
+                                        nq, nkv, d, scale, window, splits, **mask)
         x, hx = inputs.extra, inputs.plan.extra
         n_single = int(hx["attention.single_tokens"].size)
         if ops.attention_prefill_supported(nq, nkv, d) and (n_single == 0 or (
@@ -133,7 +144,7 @@ def paged_attention(qkv: torch.Tensor, inputs, group, cache, nq: int, nkv: int, 
             # a mixed step: prompt portions through the prefill kernel, decoded tokens through the
             # decode kernel, both writing their rows of one output
             out = torch.empty((inputs.num_tokens, nq * d), dtype=qkv.dtype, device=qkv.device)
-            if ops.attention_prefill_tc_supported(nq, nkv, d, P) and qkv.stride(0) % 8 == 0:
+            if windowed_only and ops.attention_prefill_tc_supported(nq, nkv, d, P) and qkv.stride(0) % 8 == 0:
                 # long rows on the tcgen05 kernel (tiles of 128 queries), short ones on the mma.sync kernel
                 if hx["attention.q_tiles_large"].shape[0]:
                     ops.attention_prefill_tc(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,
@@ -142,21 +153,20 @@ def paged_attention(qkv: torch.Tensor, inputs, group, cache, nq: int, nkv: int, 
                 if hx["attention.q_tiles_small"].shape[0]:
                     ops.attention_prefill(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,
                                           group.page_base, inputs.row_start, inputs.row_pos, x["attention.q_tiles_small"],
-                                          inputs.num_tokens, nq, nkv, d, scale, window, out=out)
+                                          inputs.num_tokens, nq, nkv, d, scale, window, out=out, **mask)
             elif hx["attention.q_tiles"].shape[0]:
                 ops.attention_prefill(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,
                                       group.page_base, inputs.row_start, inputs.row_pos, x["attention.q_tiles"],
-                                      inputs.num_tokens, nq, nkv, d, scale, window, out=out)
+                                      inputs.num_tokens, nq, nkv, d, scale, window, out=out, **mask)
             if n_single:
-                bound = group.block_table.shape[1] * P
-                if window:
-                    bound = min(bound, window)
+                bound = _key_bound(group.block_table.shape[1] * P, window, chunk, keep_first)
                 ops.attention_decode(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,
                                      group.page_base, inputs.token_row, inputs.positions, inputs.num_tokens,
                                      nq, nkv, d, scale, window,
-                                     decode_splits(n_single, nkv, bound, d, sm_count(qkv.device), _merge_free(nq, nkv, d, P)),
-                                     token_list=x["attention.single_tokens"], out=out)
+                                     decode_splits(n_single, nkv, bound, d, sm_count(qkv.device),
+                                                   _merge_free(nq, nkv, d, P) if windowed_only else 1),
+                                     token_list=x["attention.single_tokens"], out=out, **mask)
             return out
     return ops.attention_plain(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,
                                group.page_base, inputs.token_row, inputs.positions, inputs.num_tokens,
-                               nq, nkv, d, scale, window)
+                               nq, nkv, d, scale, window, value_dim=value_dim, **mask)

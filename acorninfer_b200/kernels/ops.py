@@ -88,17 +88,29 @@ def error_word_selftest(point: int) -> None:
 
 
 class _Sigs:
-    acorn_embed = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    acorn_embed = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
     acorn_patch_tokens = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
     acorn_add_rmsnorm = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]
-    acorn_swiglu = [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+    acorn_swiglu = [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
+    acorn_add_layernorm = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
+                           c_int, c_void_p]
+    acorn_add_into = [c_void_p, c_void_p, c_int64, c_int, c_void_p]
+    acorn_head_gate = [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_float, c_int, c_void_p]
+    acorn_ssm_prep = [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p,
+                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
+    acorn_silu_rows = [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_void_p]
+    acorn_linear_scan = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
+                         c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                         c_int, c_void_p]
+    acorn_gated_norm = [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_float, c_int,
+                        c_float, c_int, c_void_p]
     acorn_cast = [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
     acorn_qk_rope_kv = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-                        c_int, c_void_p]
+                        c_int, c_int64, c_int, c_int, c_void_p]
     acorn_attention_plain = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
-                             c_int, c_void_p, c_void_p]
+                             c_int, c_void_p, c_int, c_int, c_int, c_void_p]
     acorn_bigram_add = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                         c_int, c_int, c_int, c_int, c_void_p]
     acorn_rmsnorm_add = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]
@@ -130,7 +142,7 @@ class _Sigs:
                          c_void_p, c_void_p, c_float, c_void_p]
     acorn_attention_decode = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                               c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-                              c_int, c_void_p, c_void_p, c_void_p]
+                              c_int, c_void_p, c_void_p, c_int, c_int, c_void_p]
     acorn_attention_decode_supported = [c_int, c_int, c_int]
     acorn_attention_decode_tma_main = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                                        c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
@@ -141,7 +153,7 @@ class _Sigs:
     acorn_attention_decode_merge = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
     acorn_attention_prefill = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-                               c_void_p]
+                               c_int, c_int, c_void_p]
     acorn_attention_prefill_supported = [c_int, c_int, c_int]
     acorn_gemm_tc = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
                      c_void_p]
@@ -302,8 +314,8 @@ def _ptr(t: torch.Tensor | None):
 # ------------------------------------------------------------------ elementwise / norm
 
 
-def embed(ids: torch.Tensor, table: torch.Tensor, out32: torch.Tensor | None = None) -> torch.Tensor:
-    """out32[t] = table[ids[t]] as float32.  ids int32 [T]; table [V, H]."""
+def embed(ids: torch.Tensor, table: torch.Tensor, out32: torch.Tensor | None = None, scale: float = 1.0) -> torch.Tensor:
+    """out32[t] = table[ids[t]] * scale as float32.  ids int32 [T]; table [V, H]."""
     _check(ids, "ids", torch.int32, 1)
     _check(table, "table", None, 2)
     T, H = ids.numel(), table.shape[1]
@@ -311,7 +323,7 @@ def embed(ids: torch.Tensor, table: torch.Tensor, out32: torch.Tensor | None = N
         out32 = torch.empty((T, H), dtype=torch.float32, device=table.device)
     _check(out32, "out32", torch.float32, 2)
     _ok(lib().acorn_embed(ids.data_ptr(), table.data_ptr(), out32.data_ptr(), T, H, dtype_code(table.dtype),
-                          _stream()), "embed")
+                          float(scale), _stream()), "embed")
     return out32
 
 
@@ -355,8 +367,12 @@ def add_rmsnorm(resid32: torch.Tensor, delta: torch.Tensor | None, weight32: tor
     return out
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None, block: int | None = None) -> torch.Tensor:
-    """silu(gate) * up.  A row holds, per block of ``block`` outputs, the gate values then the up
+GLU_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None, block: int | None = None,
+           activation: str = "silu") -> torch.Tensor:
+    """act(gate) * up, act silu or the tanh form of gelu.  A row holds, per block of ``block`` outputs, the gate values then the up
     values; the default (block = I) is the plain layout ``[gate | up]``."""
     _check(gate_up, "gate_up", None, 2)
     T, two_i = gate_up.shape
@@ -369,7 +385,7 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None, block: int | 
         out = torch.empty((T, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
     _check(out, "out", gate_up.dtype, 2)
     _ok(lib().acorn_swiglu(gate_up.data_ptr(), out.data_ptr(), T, two_i // 2, block, dtype_code(gate_up.dtype),
-                           _stream()), "swiglu")
+                           GLU_ACTIVATIONS[activation], _stream()), "swiglu")
     return out
 
 
@@ -390,12 +406,19 @@ def qk_rope_kv(qkv: torch.Tensor, q_weight32: torch.Tensor | None, k_weight32: t
                inv_freq: torch.Tensor, positions: torch.Tensor, token_row: torch.Tensor,
                block_table: torch.Tensor, page_base: torch.Tensor, k_pages: torch.Tensor | None,
                v_pages: torch.Tensor | None, num_heads: int, num_kv_heads: int, head_dim: int,
-               rotary_dim: int, interleaved: bool, eps: float, write_kv: bool = True) -> None:
-    """Per-head q/k norm, rotary encoding, K/V page write; q is updated in place inside ``qkv``."""
+               rotary_dim: int, interleaved: bool, eps: float, write_kv: bool = True,
+               value_dim: int | None = None, values_from_keys: bool = False) -> None:
+    """Per-head q/k norm, rotary encoding, K/V page write; q is updated in place inside ``qkv``.
+    ``value_dim``: width of a value head where it is not ``head_dim`` (the value pages then hold rows of
+    that width).  ``values_from_keys``: the values are the keys as projected, before norm and rotation; a
+    row of ``qkv`` is then ``[q | k]``.  A row may be wider than its heads (further columns are ignored)."""
     _check(qkv, "qkv", None, 2)
     T = qkv.shape[0]
-    if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
-        raise KernelError(f"qkv width {qkv.shape[1]} != (nq + 2 nkv) * d")
+    dv = head_dim if value_dim is None else int(value_dim)
+    if values_from_keys and dv != head_dim:
+        raise KernelError("qk_rope_kv: values taken from the keys have the keys' width")
+    if qkv.shape[1] < (num_heads + num_kv_heads) * head_dim + (0 if values_from_keys else num_kv_heads * dv):
+        raise KernelError(f"qkv width {qkv.shape[1]} < nq d + nkv d + nkv dv")
     if head_dim > 1024 or rotary_dim > head_dim or rotary_dim % 2:
         raise KernelError(f"head_dim {head_dim} / rotary_dim {rotary_dim} not supported (d <= 1024, even rotary_dim <= d)")
     _check(inv_freq, "inv_freq", torch.float32, 1)
@@ -413,14 +436,17 @@ def qk_rope_kv(qkv: torch.Tensor, q_weight32: torch.Tensor | None, k_weight32: t
     if write_kv:
         _check(k_pages, "k_pages", qkv.dtype, 4)
         _check(v_pages, "v_pages", qkv.dtype, 4)
-        if k_pages.shape[1] != num_kv_heads or k_pages.shape[3] != head_dim or v_pages.shape != k_pages.shape:
-            raise KernelError(f"cache pages {tuple(k_pages.shape)} do not fit nkv={num_kv_heads}, d={head_dim}")
+        if k_pages.shape[1] != num_kv_heads or k_pages.shape[3] != head_dim or \
+                tuple(v_pages.shape) != (*k_pages.shape[:3], dv):
+            raise KernelError(f"cache pages {tuple(k_pages.shape)} / {tuple(v_pages.shape)} do not fit "
+                              f"nkv={num_kv_heads}, d={head_dim}, dv={dv}")
         P = k_pages.shape[2]
     _ok(lib().acorn_qk_rope_kv(qkv.data_ptr(), _ptr(q_weight32), _ptr(k_weight32), inv_freq.data_ptr(),
                                positions.data_ptr(), token_row.data_ptr(), block_table.data_ptr(),
                                page_base.data_ptr(), block_table.stride(0), _ptr(k_pages), _ptr(v_pages), T,
                                num_heads, num_kv_heads, head_dim, rotary_dim, 1 if interleaved else 0,
-                               max(P, 1), float(eps), 1 if write_kv else 0, dtype_code(qkv.dtype), _stream()),
+                               max(P, 1), float(eps), 1 if write_kv else 0, dtype_code(qkv.dtype), qkv.stride(0), dv,
+                               1 if values_from_keys else 0, _stream()),
         "qk_rope_kv")
 
 
@@ -428,14 +454,17 @@ def attention_plain(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pag
                     block_table: torch.Tensor, page_base: torch.Tensor, token_row: torch.Tensor,
                     positions: torch.Tensor, num_tokens: int, num_heads: int, num_kv_heads: int, head_dim: int,
                     scale: float, window: int | None, out: torch.Tensor | None = None,
-                    value_dim: int | None = None, sink32: torch.Tensor | None = None) -> torch.Tensor:
+                    value_dim: int | None = None, sink32: torch.Tensor | None = None, chunk: int | None = None,
+                    keep_first: int = 0) -> torch.Tensor:
     """Paged causal attention for any mix of rows; ``q`` may be the head of a wider buffer
     (row stride ``q_stride`` elements).  Returns [tokens, nq * value_dim].  ``value_dim`` (default
     ``head_dim``): the leading entries of a value row that are summed; ``v_pages`` may be ``k_pages``
-    itself.  ``sink32`` (float32 [nq]): a learned term exp(sink) per query head in the softmax denominator."""
+    itself.  ``sink32`` (float32 [nq]): a learned term exp(sink) per query head in the softmax denominator.
+    ``window`` / ``chunk`` / ``keep_first``: which earlier keys a query reads (the last ``window``
+    positions; those of its own block of ``chunk`` positions; and always the request's first ``keep_first``)."""
     dv = head_dim if value_dim is None else int(value_dim)
-    if not (1 <= dv <= head_dim):
-        raise KernelError(f"value_dim must be in 1..head_dim, got {dv}")
+    if not (1 <= dv <= v_pages.shape[3]):
+        raise KernelError(f"value_dim must be in 1..{v_pages.shape[3]} (the value rows' width), got {dv}")
     if sink32 is not None:
         _check(sink32, "sink", torch.float32, 1)
         if sink32.numel() != num_heads:
@@ -454,7 +483,8 @@ def attention_plain(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pag
                                     v_pages.data_ptr(), block_table.data_ptr(), page_base.data_ptr(),
                                     block_table.stride(0), token_row.data_ptr(), positions.data_ptr(),
                                     num_tokens, num_heads, num_kv_heads, head_dim, k_pages.shape[2],
-                                    float(scale), int(window or 0), dtype_code(q.dtype), dv, _ptr(sink32), _stream()),
+                                    float(scale), int(window or 0), dtype_code(q.dtype), dv, _ptr(sink32),
+                                    int(chunk or 0), int(keep_first or 0), v_pages.shape[3], _stream()),
         "attention_plain")
     return out
 
@@ -472,7 +502,7 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pa
                      positions: torch.Tensor, num_tokens: int, num_heads: int, num_kv_heads: int, head_dim: int,
                      scale: float, window: int | None, num_splits: int, token_list: torch.Tensor | None = None,
                      out: torch.Tensor | None = None, scratch: tuple | None = None,
-                     use_tma: bool | None = None) -> torch.Tensor:
+                     use_tma: bool | None = None, chunk: int | None = None, keep_first: int = 0) -> torch.Tensor:
     """Split-K decode attention (bfloat16) for single-token rows: the tokens 0..num_tokens-1, or
     those listed in ``token_list``.  ``out`` is [all tokens of the step, nq * d]; rows of tokens
     not handled are left as they are.  ``scratch`` = (part_o float32 [n, nq, splits, d],
@@ -491,6 +521,10 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pa
     if out is None:
         out = torch.empty((num_tokens, num_heads * head_dim), dtype=q.dtype, device=q.device)
     P = k_pages.shape[2]
+    if chunk or keep_first:
+        if use_tma:
+            raise KernelError("attention_decode: the TMA kernel knows windows only")
+        use_tma = False
     if use_tma is None:
         use_tma = bool(lib().acorn_attention_decode_tma_supported(num_heads, num_kv_heads, head_dim, P))
     # the TMA kernel merges up to sixteen splits itself (a cluster, through shared memory): no scratch
@@ -521,7 +555,8 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pa
                                      block_table.data_ptr(), page_base.data_ptr(), block_table.stride(0),
                                      token_row.data_ptr(), positions.data_ptr(), _ptr(token_list), n, num_heads,
                                      num_kv_heads, head_dim, P, float(scale), int(window or 0),
-                                     num_splits, _ptr(part_o), _ptr(part_lse), _stream()), "attention_decode")
+                                     num_splits, _ptr(part_o), _ptr(part_lse), int(chunk or 0), int(keep_first or 0),
+                                     _stream()), "attention_decode")
     return out
 
 
@@ -533,7 +568,7 @@ def attention_prefill(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_p
                       block_table: torch.Tensor, page_base: torch.Tensor, row_start: torch.Tensor,
                       row_pos: torch.Tensor, tiles: torch.Tensor, num_tokens: int, num_heads: int,
                       num_kv_heads: int, head_dim: int, scale: float, window: int | None,
-                      out: torch.Tensor | None = None) -> torch.Tensor:
+                      out: torch.Tensor | None = None, chunk: int | None = None, keep_first: int = 0) -> torch.Tensor:
     """Tensor-core prefill attention (bfloat16) for the query tiles listed in ``tiles``
     (int32 [n, 2]: row, first token within the row; 64 tokens a tile at most)."""
     if q.dtype != torch.bfloat16:
@@ -550,7 +585,8 @@ def attention_prefill(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_p
                                       block_table.data_ptr(), page_base.data_ptr(), block_table.stride(0),
                                       row_start.data_ptr(), row_pos.data_ptr(), tiles.data_ptr(), tiles.shape[0],
                                       num_heads, num_kv_heads, head_dim, k_pages.shape[2], float(scale),
-                                      int(window or 0), _stream()), "attention_prefill")
+                                      int(window or 0), int(chunk or 0), int(keep_first or 0), _stream()),
+        "attention_prefill")
     return out
 
 
@@ -1190,6 +1226,179 @@ def delta_out(o32: torch.Tensor, gate32: torch.Tensor, weight32: torch.Tensor, e
     _ok(lib().acorn_delta_out(o32.data_ptr(), gate32.data_ptr(), weight32.data_ptr(), y.data_ptr(), T, H, vdim, float(eps),
                               dtype_code(dtype), _stream()), "delta_out")
     return y
+
+
+# ------------------------------------------------------------------ layer norm, sums, head gates
+
+
+def add_layernorm(resid32: torch.Tensor, delta, weight32: torch.Tensor, bias32: torch.Tensor | None, eps: float,
+                  out_dtype: torch.dtype, row_idx: torch.Tensor | None = None,
+                  out: torch.Tensor | None = None) -> torch.Tensor:
+    """resid32 += delta (in place, unless row_idx is given); returns the layer norm of it,
+    ``(x - mean) / sqrt(var + eps) * weight + bias``.  ``delta``: None, a tensor, or a ``DeltaPair`` (both are added)."""
+    _check(resid32, "resid32", torch.float32, 2)
+    _check(weight32, "weight", torch.float32, 1)
+    H = resid32.shape[1]
+    if weight32.numel() != H or (bias32 is not None and bias32.numel() != H):
+        raise KernelError(f"norm weight / bias do not have the width {H}")
+    d1, d2 = (delta.a, delta.b) if isinstance(delta, DeltaPair) else (delta, None)
+    for d in (d1, d2):
+        if d is not None:
+            _check(d, "delta", out_dtype, 2)
+            if d.shape != resid32.shape:
+                raise KernelError(f"delta {tuple(d.shape)} does not match the residual {tuple(resid32.shape)}")
+    rows = resid32.shape[0]
+    if row_idx is not None:
+        _check(row_idx, "row_idx", torch.int32, 1)
+        rows = row_idx.numel()
+    if out is None:
+        out = torch.empty((rows, H), dtype=out_dtype, device=resid32.device)
+    _check(out, "out", out_dtype, 2)
+    _ok(lib().acorn_add_layernorm(resid32.data_ptr(), _ptr(d1), _ptr(d2), weight32.data_ptr(), _ptr(bias32),
+                                  out.data_ptr(), _ptr(row_idx), rows, H, float(eps), dtype_code(out_dtype), _stream()),
+        "add_layernorm")
+    return out
+
+
+class DeltaPair:
+    """Two results that are both still to be added to the residual stream (the mixer's and the
+    feed-forward's of a block whose sublayers read the same normed rows)."""
+
+    def __init__(self, a: torch.Tensor, b: torch.Tensor):
+        self.a, self.b = a, b
+
+
+def add_into(resid32: torch.Tensor, delta: torch.Tensor) -> None:
+    """resid32 += delta (float32 sum, in place)."""
+    _check(resid32, "resid32", torch.float32)
+    _check(delta, "delta")
+    if delta.shape != resid32.shape:
+        raise KernelError(f"add_into: {tuple(delta.shape)} onto {tuple(resid32.shape)}")
+    _ok(lib().acorn_add_into(resid32.data_ptr(), delta.data_ptr(), resid32.numel(), dtype_code(delta.dtype), _stream()),
+        "add_into")
+
+
+def fold_pair(resid32: torch.Tensor, delta):
+    """A ``DeltaPair`` as one pending result: the first is added to the stream now, the second handed on."""
+    if isinstance(delta, DeltaPair):
+        add_into(resid32, delta.a)
+        return delta.b
+    return delta
+
+
+def head_gate(x: torch.Tensor, gate: torch.Tensor | None, heads: int, scale: float = 1.0,
+              out: torch.Tensor | None = None) -> torch.Tensor:
+    """x [T, heads * d] times scale * sigmoid(gate[:, h]) per head, in place or into ``out`` (rows of another
+    buffer).  ``gate`` [T, >= heads] may be a slice of a wider buffer; None: x * scale."""
+    _check(x, "x", None, 2)
+    out = x if out is None else out
+    _rows2(out, "out", x.dtype)
+    if out.shape != x.shape:
+        raise KernelError(f"head_gate: out {tuple(out.shape)} for x {tuple(x.shape)}")
+    if gate is not None and (gate.dtype != x.dtype or gate.dim() != 2 or gate.stride(1) != 1
+                             or gate.shape[0] != x.shape[0] or gate.shape[1] < heads):
+        raise KernelError(f"head_gate: gate {tuple(gate.shape)} {gate.dtype} does not fit x {tuple(x.shape)} {x.dtype}")
+    if x.shape[1] % heads:
+        raise KernelError("head_gate: the row is not a whole number of heads")
+    _ok(lib().acorn_head_gate(x.data_ptr(), _ptr(gate), gate.stride(0) if gate is not None else 0, out.data_ptr(),
+                              out.stride(0), x.shape[0], heads, x.shape[1] // heads, float(scale), dtype_code(x.dtype),
+                              _stream()), "head_gate")
+    return out
+
+
+# ------------------------------------------------------------------ linear recurrences (state space, linear attention)
+
+
+def _rows2(t: torch.Tensor, name: str, dtype=None):
+    """A [T, W] view whose rows may be strided (a slice of a wider buffer)."""
+    if t.dim() != 2 or t.stride(1) != 1 or (dtype is not None and t.dtype != dtype) or not t.is_cuda:
+        raise KernelError(f"{name}: expected a 2-d {dtype or ''} device tensor with unit column stride, got "
+                          f"{tuple(t.shape)} {t.dtype} strides {t.stride()}")
+
+
+def ssm_prep(proj: torch.Tensor, conv_col: int, dt_col: int, conv_w32: torch.Tensor, conv_b32: torch.Tensor | None,
+             state: torch.Tensor, conv_off: int, a_log32: torch.Tensor, dt_bias32: torch.Tensor,
+             token_row: torch.Tensor, row_start: torch.Tensor, row_slot: torch.Tensor, taps: int):
+    """Of a projection ``proj`` [T, W]: the short causal convolution (``taps`` weights per channel, the last for
+    the current token; inputs before the step from the request's state at ``conv_off``) with bias and silu of the
+    ``C`` channels from column ``conv_col``, and of the ``H`` columns from ``dt_col`` the step sizes
+    ``softplus(. + dt_bias)`` and the decays ``exp(-exp(A_log) dt)``.  Returns float32 (act [T, C], dt [T, H], decay [T, H])."""
+    _rows2(proj, "proj")
+    _check(state, "state", torch.float32, 2)
+    _check(conv_w32, "conv weights", torch.float32, 2)
+    T = proj.shape[0]
+    C, H = conv_w32.shape[0], a_log32.numel()
+    if conv_w32.shape[1] != taps or (conv_b32 is not None and conv_b32.numel() != C) or dt_bias32.numel() != H:
+        raise KernelError("ssm_prep: convolution or step-size parameters do not fit")
+    if conv_col + C > proj.shape[1] or dt_col + H > proj.shape[1] or state.shape[1] < conv_off + (taps - 1) * C:
+        raise KernelError("ssm_prep: columns beyond the projection, or a state too small for the convolution's memory")
+    f = lambda *shape: torch.empty(shape, dtype=torch.float32, device=proj.device)
+    act, dt, decay = f(T, C), f(T, H), f(T, H)
+    _ok(lib().acorn_ssm_prep(proj.data_ptr(), proj.stride(0), int(conv_col), int(dt_col), conv_w32.data_ptr(),
+                             _ptr(conv_b32), state.data_ptr(), state.stride(0), int(conv_off), a_log32.data_ptr(),
+                             dt_bias32.data_ptr(), token_row.data_ptr(), row_start.data_ptr(), row_slot.data_ptr(),
+                             act.data_ptr(), dt.data_ptr(), decay.data_ptr(), T, C, H, taps, dtype_code(proj.dtype),
+                             _stream()), "ssm_prep")
+    return act, dt, decay
+
+
+def silu_rows(x: torch.Tensor) -> torch.Tensor:
+    """silu(x) as float32 [T, W]; ``x`` may be a column slice of a wider buffer."""
+    _rows2(x, "x")
+    out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+    _ok(lib().acorn_silu_rows(x.data_ptr(), x.stride(0), out.data_ptr(), x.shape[0], x.shape[1], dtype_code(x.dtype),
+                              _stream()), "silu_rows")
+    return out
+
+
+def linear_scan(b: torch.Tensor, c: torch.Tensor, x: torch.Tensor, decay: torch.Tensor, w: torch.Tensor | None,
+                skip32: torch.Tensor | None, state: torch.Tensor, state_off: int, row_start: torch.Tensor,
+                row_slot: torch.Tensor, num_rows: int, heads: int, groups: int, n: int, v: int) -> torch.Tensor:
+    """Per head ``S <- a S + b (w x)^T; y = S^T c + skip x`` over every row's tokens, from the state in the
+    row's slot (``[heads, v, n]`` float32 at ``state_off``, updated in place).  ``b``, ``c`` [T, groups * n],
+    ``x`` [T, heads * v] float32 (column slices allowed); ``decay`` [T, heads] per token or [heads] for all;
+    ``w`` [T, heads] or None.  Returns float32 y [T, heads * v]."""
+    for t, name in ((b, "b"), (c, "c"), (x, "x")):
+        _rows2(t, name, torch.float32)
+    _check(state, "state", torch.float32, 2)
+    T = x.shape[0]
+    if b.shape != (T, groups * n) or c.shape != (T, groups * n) or x.shape[1] != heads * v:
+        raise KernelError(f"linear_scan: b {tuple(b.shape)}, c {tuple(c.shape)}, x {tuple(x.shape)} do not fit "
+                          f"heads={heads}, groups={groups}, n={n}, v={v}")
+    if heads % groups or n > 512 or state.shape[1] < state_off + heads * n * v:
+        raise KernelError("linear_scan: sizes not supported (groups must divide heads, n <= 512) or state too small")
+    if decay.dtype != torch.float32 or (decay.dim() == 1 and decay.numel() != heads) or \
+            (decay.dim() == 2 and (decay.shape != (T, heads) or decay.stride(1) != 1)):
+        raise KernelError(f"linear_scan: decay {tuple(decay.shape)} is neither [T, heads] nor [heads]")
+    if w is not None:
+        _rows2(w, "w", torch.float32)
+    if skip32 is not None:
+        _check(skip32, "skip", torch.float32, 1)
+    y = torch.empty((T, heads * v), dtype=torch.float32, device=x.device)
+    _ok(lib().acorn_linear_scan(b.data_ptr(), b.stride(0), c.data_ptr(), c.stride(0), x.data_ptr(), x.stride(0),
+                                decay.data_ptr(), decay.stride(0) if decay.dim() == 2 else 0, _ptr(w),
+                                w.stride(0) if w is not None else 0, _ptr(skip32), state.data_ptr(), state.stride(0),
+                                int(state_off), y.data_ptr(), row_start.data_ptr(), row_slot.data_ptr(), num_rows, heads,
+                                groups, n, v, _stream()), "linear_scan")
+    return y
+
+
+def gated_norm(y32: torch.Tensor, gate: torch.Tensor, weight32: torch.Tensor, eps: float, groups: int, gate_first: bool,
+               out: torch.Tensor, out_scale: float = 1.0) -> torch.Tensor:
+    """RMS norm of ``y32`` [T, W] in ``groups`` equal parts times ``weight32``, with a gate ``z`` [T, W]:
+    ``gate_first``: ``norm(y silu(z))``; else ``norm(y) sigmoid(z)``.  Times ``out_scale``, rounded once into ``out``
+    [T, W] (a column slice of a wider buffer is allowed, as for ``gate``)."""
+    _check(y32, "y", torch.float32, 2)
+    _rows2(gate, "gate")
+    _rows2(out, "out", gate.dtype)
+    _check(weight32, "weight", torch.float32, 1)
+    T, W = y32.shape
+    if gate.shape != (T, W) or out.shape != (T, W) or weight32.numel() != W or W % groups:
+        raise KernelError(f"gated_norm: y {tuple(y32.shape)}, gate {tuple(gate.shape)}, out {tuple(out.shape)}, groups {groups}")
+    _ok(lib().acorn_gated_norm(y32.data_ptr(), gate.data_ptr(), gate.stride(0), weight32.data_ptr(), out.data_ptr(),
+                               out.stride(0), T, W, groups, float(eps), 0 if gate_first else 1, float(out_scale),
+                               dtype_code(gate.dtype), _stream()), "gated_norm")
+    return out
 
 
 # ------------------------------------------------------------------ routed experts

@@ -160,7 +160,7 @@ class Decoder:
 
     def forward(self, inputs, caches: list[EntryCache]) -> torch.Tensor | None:
         """Runs the step's tokens; returns float32 logits [wanted, vocab] (None if none wanted)."""
-        resid32 = ops.embed(inputs.token_ids, self.embedding)
+        resid32 = ops.embed(inputs.token_ids, self.embedding, scale=self.spec.embedding_scale)
         for stage in self.stages["after_embedding"]:
             resid32 = stage.forward(resid32, inputs)
         delta = None
@@ -170,6 +170,11 @@ class Decoder:
             # works on selected rows only and keeps its own kernel)
             nxt = self.blocks[sched[i + 1].layer].first_norm(inputs.num_tokens) if i + 1 < len(sched) else None
             resid32, delta = self.blocks[e.layer].forward(resid32, delta, inputs, caches[i], next_norm=nxt)
+            # two pending results (a block whose sublayers run side by side): whoever comes next adds both, or
+            # the first is added here
+            taker = self.blocks[sched[i + 1].layer] if i + 1 < len(sched) else self.final_norm
+            if isinstance(delta, ops.DeltaPair) and not getattr(taker, "accepts_pair", False):
+                delta = ops.fold_pair(resid32, delta)
         if inputs.num_logits == 0:
             return None
         if isinstance(delta, ops.RoundedRows):          # the last block already added its result

@@ -2,14 +2,21 @@
 
 Per token: q/k/v projections (no bias), optional per-head RMSNorm of q and k (one weight
 of head size shared by all heads), position encoding, K/V written to the request's
-pages, causal attention of every query over the keys of its own request (all of them,
-or a window), output projection.  Reference: ``Qwen3Attention`` in
+pages, causal attention of every query over the keys of its own request, output projection.
+Reference: ``Qwen3Attention`` in
 ``acorninfer/models/qwen3.py:106-152`` and its decode form ``:154-233``; scale
 ``head_dim ** -0.5`` (``acorninfer/ops/paged_attention.py:147``); query head h uses kv head
 ``h // (nq / nkv)`` (``acorninfer/models/qwen3.py:98-103``).
 
-All sizes are parameters.  The q, k, v matrices are concatenated when bound so that one
-matrix product yields ``[tokens, (nq + 2 nkv) * d]``.  A run that reads another run's
+Which earlier keys a query reads: all of them; the last ``window`` positions; those of its own
+block of ``chunk`` positions (blocks counted from position 0 of the request); and, whatever the
+rule, the request's first ``keep_first`` keys.  Options: value heads of a width of their own
+(``value_dim``); values that are the keys as projected, before norm and rotation
+(``values_from_keys``: no value matrix); a gate per head on the heads' outputs,
+``sigmoid(W_g x)_h``, a function of the mixer's input (``head_gate``).
+
+All sizes are parameters.  The q, k, v (and gate) matrices are concatenated when bound so that one
+matrix product yields a token's whole row.  A run that reads another run's
 cache (``cache.write`` false) computes queries only.
 """
 
@@ -21,6 +28,9 @@ from ..kernels import ops
 from ..kernels import attention as attn_kernels
 from .base import MIXERS, BuildContext, CacheNeeds, KVNeeds, Mixer, TensorSpec
 
+_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+          "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "gate": "g_proj.weight"}
+
 
 @MIXERS.register("attention")
 class Attention(Mixer):
@@ -30,62 +40,91 @@ class Attention(Mixer):
 
     def __init__(self, ctx: BuildContext, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: str | None, scale: float, qk_norm_eps: float | None = None,
-                 window: int | None = None):
+                 window: int | None = None, chunk: int | None = None, keep_first: int = 0,
+                 value_dim: int | None = None, values_from_keys: bool = False, head_gate: bool = False,
+                 names: dict | None = None):
+        """``names``: the tensors' names relative to the part's prefix (keys q, k, v, o, q_norm, k_norm, gate)."""
         if num_heads % num_kv_heads:
             raise ValueError(f"num_heads ({num_heads}) must be a multiple of num_kv_heads ({num_kv_heads})")
-        if window is not None and window < 1:
-            raise ValueError(f"window must be >= 1 or None, got {window}")
+        for what, n in (("window", window), ("chunk", chunk)):
+            if n is not None and n < 1:
+                raise ValueError(f"{what} must be >= 1 or None, got {n}")
+        if keep_first < 0:
+            raise ValueError(f"keep_first must be >= 0, got {keep_first}")
         self.ctx = ctx
         self.hidden_size = hidden_size
         self.nq, self.nkv, self.d = num_heads, num_kv_heads, head_dim
+        self.dv = head_dim if value_dim is None else value_dim
+        if values_from_keys and self.dv != head_dim:
+            raise ValueError(f"values taken from the keys have the keys' width {head_dim}, not {self.dv}")
+        self.values_from_keys, self.head_gate = values_from_keys, head_gate
         self.scale = float(scale)
         self.qk_norm_eps = qk_norm_eps
-        self.window = window
+        self.window, self.chunk, self.keep_first = window, chunk, keep_first
+        self.names = {**_NAMES, **(names or {})}
         self.position = ctx.positions[position] if position is not None else None
         if self.position is not None and self.position.head_dim != head_dim:
             raise ValueError("position encoding was built for another head size")
+        # the plain arrangement [q | k | v] of equal head sizes, which the fused products take
+        self.plain = not (values_from_keys or head_gate) and self.dv == head_dim
+        self.gate_col = (self.nq + self.nkv) * self.d + (0 if values_from_keys else self.nkv * self.dv)
         self.w_qkv = self.w_o = self.q_norm32 = self.k_norm32 = None
 
     def tensor_specs(self):
+        n = self.names
         specs = {
-            "q_proj.weight": TensorSpec((self.nq * self.d, self.hidden_size)),
-            "k_proj.weight": TensorSpec((self.nkv * self.d, self.hidden_size)),
-            "v_proj.weight": TensorSpec((self.nkv * self.d, self.hidden_size)),
-            "o_proj.weight": TensorSpec((self.hidden_size, self.nq * self.d)),
+            n["q"]: TensorSpec((self.nq * self.d, self.hidden_size)),
+            n["k"]: TensorSpec((self.nkv * self.d, self.hidden_size)),
+            n["o"]: TensorSpec((self.hidden_size, self.nq * self.dv)),
         }
+        if not self.values_from_keys:
+            specs[n["v"]] = TensorSpec((self.nkv * self.dv, self.hidden_size))
+        if self.head_gate:
+            specs[n["gate"]] = TensorSpec((self.nq, self.hidden_size))
         if self.qk_norm_eps is not None:
-            specs["q_norm.weight"] = TensorSpec((self.d,), "norm")
-            specs["k_norm.weight"] = TensorSpec((self.d,), "norm")
+            specs[n["q_norm"]] = TensorSpec((self.d,), "norm")
+            specs[n["k_norm"]] = TensorSpec((self.d,), "norm")
         return specs
 
     def bind(self, tensors):
-        parts = [tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]]
+        n = self.names
+        parts = [tensors[n["q"]], tensors[n["k"]]]
+        if not self.values_from_keys:
+            parts.append(tensors[n["v"]])
+        if self.head_gate:
+            # padded with zero rows to a multiple of 8, so that a token's row keeps 16-byte alignment
+            g = tensors[n["gate"]]
+            pad = (-self.nq) % 8
+            parts.append(torch.cat([g, g.new_zeros((pad, g.shape[1]))], dim=0) if pad else g)
         dtype = parts[0].dtype if all(p.dtype == parts[0].dtype for p in parts) else torch.float32
         self.w_qkv = torch.cat([p.to(dtype) for p in parts], dim=0).contiguous()
-        self.w_o = tensors["o_proj.weight"].contiguous()
+        self.w_o = tensors[n["o"]].contiguous()
         if self.qk_norm_eps is not None:
-            self.q_norm32 = tensors["q_norm.weight"].to(torch.float32).contiguous()
-            self.k_norm32 = tensors["k_norm.weight"].to(torch.float32).contiguous()
+            self.q_norm32 = tensors[n["q_norm"]].to(torch.float32).contiguous()
+            self.k_norm32 = tensors[n["k_norm"]].to(torch.float32).contiguous()
 
     def cache_needs(self):
-        return CacheNeeds(kv=KVNeeds(self.nkv, self.d, self.window))
+        return CacheNeeds(kv=KVNeeds(self.nkv, self.d, self.window, chunk=self.chunk, keep_first=self.keep_first,
+                                     value_dim=None if self.dv == self.d else self.dv))
 
     def step_arrays(self):
         return attn_kernels.STEP_ARRAYS
 
     def fusable(self, num_rows):
-        return (self._rows_fuse(num_rows) and self.w_qkv.dtype == torch.bfloat16
+        return (self.plain and self._rows_fuse(num_rows) and self.w_qkv.dtype == torch.bfloat16
                 and self.w_o.dtype == torch.bfloat16 and self.hidden_size % 8 == 0 and (self.nq * self.d) % 8 == 0)
 
     def _rows_fuse(self, num_rows):
         widths = ((self.nq + 2 * self.nkv) * self.d, self.hidden_size)         # of the q/k/v product and of the o product
         return ops.fused_rows_ok(num_rows, self.ctx.dtype, widths, ops.device_sms(self.ctx.device))
 
-    def forward(self, x, inputs, cache, epilogue=None, residual32=None):
+    def inner(self, x, inputs, cache, out_scale: float = 1.0, out=None):
+        """Everything before the output projection: the heads' outputs [T, nq * dv] (gated, times ``out_scale``),
+        into ``out`` if given (rows of a wider buffer)."""
         g = inputs.groups[cache.group]
         pos = self.position
         rows = x.x.shape[0] if isinstance(x, ops.NormedRows) else x.shape[0]
-        if (pos is not None and self.w_qkv.dtype == torch.bfloat16 and ops.gemm_tc_supported(
+        if (self.plain and pos is not None and self.w_qkv.dtype == torch.bfloat16 and ops.gemm_tc_supported(
                 x.x if isinstance(x, ops.NormedRows) else x, self.w_qkv)
                 and self._rows_fuse(rows)
                 and ops.rope_kv_fusable(rows, self.ctx.dtype, self.d, pos.rotary_dim, pos.interleaved)):
@@ -103,9 +142,16 @@ class Attention(Mixer):
                            inputs.positions, inputs.token_row, g.block_table, g.page_base,
                            cache.k_pages, cache.v_pages, self.nq, self.nkv, self.d,
                            pos.rotary_dim if pos is not None else 0, pos.interleaved if pos is not None else False,
-                           self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, write_kv=cache.write)
-        out = attn_kernels.paged_attention(qkv, inputs, g, cache, self.nq, self.nkv, self.d, self.scale, self.window)
-        return ops.linear(out, self.w_o, out_dtype=self.ctx.dtype, epilogue=epilogue,
+                           self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, write_kv=cache.write,
+                           value_dim=self.dv, values_from_keys=self.values_from_keys)
+        heads = attn_kernels.paged_attention(qkv, inputs, g, cache, self.nq, self.nkv, self.d, self.scale, self.window,
+                                             chunk=self.chunk, keep_first=self.keep_first, value_dim=self.dv)
+        if self.head_gate or out_scale != 1.0 or out is not None:
+            return ops.head_gate(heads, qkv[:, self.gate_col:] if self.head_gate else None, self.nq, out_scale, out=out)
+        return heads
+
+    def forward(self, x, inputs, cache, epilogue=None, residual32=None):
+        return ops.linear(self.inner(x, inputs, cache), self.w_o, out_dtype=self.ctx.dtype, epilogue=epilogue,
                           residual32=residual32 if epilogue is None else None)
 
 

@@ -91,6 +91,7 @@ class ModelSpec:
     after_embedding: tuple[PartSpec, ...] = ()    # on the float32 residual stream [tokens, hidden]
     before_head: tuple[PartSpec, ...] = ()        # on the normed rows whose logits are wanted [wanted, hidden]
     after_head: tuple[PartSpec, ...] = ()         # on the float32 logits [wanted, vocab]
+    embedding_scale: float = 1.0                  # factor on the token rows as they enter the stream (not on a tied head)
 
 
 @dataclass
@@ -107,24 +108,36 @@ class BuildContext:
 @dataclass(frozen=True)
 class KVNeeds:
     """Keys and values in pages.  ``window`` None: every earlier key is read;
-    an integer w: a query at position p reads keys p-w+1 .. p.  ``dtype`` None: the engine's
-    activation dtype.  ``values`` False: one row per token and kv head only (a mixer whose values are
-    a function of its key rows, such as attention through a cached latent)."""
+    an integer w: a query at position p reads keys p-w+1 .. p.  ``chunk`` c: a query reads the keys of
+    its own block of c positions only (blocks counted from position 0).  ``keep_first`` n: the
+    request's first n keys stay readable whatever the window (the pages of such a cache are all kept).
+    ``dtype`` None: the engine's activation dtype.  ``values`` False: one row per token and kv head only
+    (a mixer whose values are a function of its key rows, such as attention through a cached latent).
+    ``value_dim``: width of a value row where it differs from ``head_dim`` (values then lie in a
+    tensor of their own)."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
     dtype: torch.dtype | None = None
     values: bool = True
+    chunk: int | None = None
+    keep_first: int = 0
+    value_dim: int | None = None
 
     @property
     def group_key(self) -> tuple:
-        return ("kv", self.num_kv_heads, self.head_dim, self.window, self.dtype, self.values)
+        return ("kv", self.num_kv_heads, self.head_dim, self.window, self.dtype, self.values, self.chunk,
+                self.keep_first, self.value_width)
+
+    @property
+    def value_width(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
 
     @property
     def layout_key(self) -> tuple:
         """What two runs must agree on for one to read the other's pages (their windows may differ)."""
-        return (self.num_kv_heads, self.head_dim, self.dtype, self.values)
+        return (self.num_kv_heads, self.head_dim, self.dtype, self.values, self.value_width)
 
 
 @dataclass(frozen=True)

@@ -9,6 +9,10 @@ where ``delta`` is what the previous block still has to add, and returns the sam
 stream itself and only their outputs are normed (Kogonex).  The sums are done here, in float32, by
 the kernel that norms the output; it also hands on the stream rounded to the activation dtype, which
 is what the next sublayer reads (``RoundedRows``).  A layer may have no feed-forward.
+
+``parallel``: ``h = norm(x); x += mixer(h) + feed_forward(h)``: one norm, both sublayers read its
+output.  Both results are added in float32: by the product that made them where it can add into the
+stream itself, else by the norm kernel of the next block (``DeltaPair``).  A layer may have no feed-forward.
 """
 
 from __future__ import annotations
@@ -95,3 +99,33 @@ class OutputNormBlock(Block):
             else:
                 h = self._rows(resid32, norm.normed_add(resid32, self.feed_forward.forward(h, inputs)))
         return resid32, ops.RoundedRows(h)
+
+
+@BLOCKS.register("parallel")
+class ParallelBlock(Block):
+    graph_safe = True
+    accepts_pair = True           # takes an ``ops.DeltaPair`` as the pending result of the block before
+
+    def __init__(self, ctx, mixer, feed_forward, norms):
+        super().__init__(mixer, feed_forward, norms)
+        if "input" not in norms:
+            raise ValueError("parallel block needs a norm named 'input'")
+        if not getattr(norms["input"], "accepts_pair", False):
+            raise ValueError("the norm of a parallel block must take two pending results (accepts_pair)")
+
+    def forward(self, resid32, delta, inputs, cache, next_norm=None):
+        if isinstance(delta, ops.RoundedRows):          # the block before added its result itself
+            delta = None
+        if isinstance(delta, ops.NormedRows):
+            raise ValueError("a parallel block cannot follow a block that fused the next norm into its last product")
+        h = self.norms["input"].add_forward(resid32, delta)
+        # each sublayer adds its result to the stream itself where its last product can (None comes back)
+        a = self.mixer.forward(h, inputs, cache, residual32=resid32) if self.mixer.adds_residual \
+            else self.mixer.forward(h, inputs, cache)
+        if self.feed_forward is None:
+            return resid32, a
+        b = self.feed_forward.forward(h, inputs, residual32=resid32) if self.feed_forward.adds_residual \
+            else self.feed_forward.forward(h, inputs)
+        if a is None or b is None:
+            return resid32, (a if b is None else b)
+        return resid32, ops.DeltaPair(a, b)

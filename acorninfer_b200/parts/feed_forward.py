@@ -1,5 +1,6 @@
-"""SwiGLU feed-forward: ``down(silu(gate(x)) * up(x))``, no bias, every token through the
-one set of matrices.  Reference: ``Qwen3MLP`` in ``acorninfer/models/qwen3.py:385-396``.
+"""Gated feed-forward: ``down(act(gate(x)) * up(x))``, no bias, every token through the
+one set of matrices; ``act`` is silu (SwiGLU) or the tanh form of gelu.  Reference: ``Qwen3MLP`` in
+``acorninfer/models/qwen3.py:385-396``.
 gate and up are concatenated when bound: one matrix product gives ``[tokens, 2 I]``.
 """
 
@@ -11,13 +12,20 @@ from ..kernels import ops
 from .base import FEED_FORWARDS, BuildContext, FeedForward, TensorSpec
 
 
+@FEED_FORWARDS.register("gated")
 @FEED_FORWARDS.register("swiglu")
 class SwiGLU(FeedForward):
     graph_safe = True
     supports_epilogue = True
     adds_residual = True
 
-    def __init__(self, ctx: BuildContext, hidden_size: int, intermediate_size: int):
+    def __init__(self, ctx: BuildContext, hidden_size: int, intermediate_size: int, activation: str = "silu",
+                 names: dict | None = None):
+        """``names``: the gate, up and down matrices' names relative to the part's prefix."""
+        if activation not in ops.GLU_ACTIVATIONS:
+            raise ValueError(f"activation must be one of {sorted(ops.GLU_ACTIVATIONS)}, got {activation!r}")
+        self.activation = activation
+        self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight", **(names or {})}
         self.ctx = ctx
         self.hidden_size = hidden_size
         self.intermediate_size = intermediate_size
@@ -29,22 +37,23 @@ class SwiGLU(FeedForward):
 
     def tensor_specs(self):
         return {
-            "gate_proj.weight": TensorSpec((self.intermediate_size, self.hidden_size)),
-            "up_proj.weight": TensorSpec((self.intermediate_size, self.hidden_size)),
-            "down_proj.weight": TensorSpec((self.hidden_size, self.intermediate_size)),
+            self.names["gate"]: TensorSpec((self.intermediate_size, self.hidden_size)),
+            self.names["up"]: TensorSpec((self.intermediate_size, self.hidden_size)),
+            self.names["down"]: TensorSpec((self.hidden_size, self.intermediate_size)),
         }
 
     def bind(self, tensors):
-        g, u = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        g, u = tensors[self.names["gate"]], tensors[self.names["up"]]
         dtype = g.dtype if g.dtype == u.dtype else torch.float32
         b, I, H = self.block, self.intermediate_size, self.hidden_size
         self.w_gate_up = torch.stack([g.to(dtype).view(I // b, b, H), u.to(dtype).view(I // b, b, H)], dim=1) \
             .reshape(2 * I, H).contiguous()
-        self.w_down = tensors["down_proj.weight"].contiguous()
+        self.w_down = tensors[self.names["down"]].contiguous()
 
     def fusable(self, num_rows):
         widths = (2 * self.intermediate_size, self.hidden_size)                 # of the gate/up product and of the down product
-        return (ops.fused_rows_ok(num_rows, self.ctx.dtype, widths, ops.device_sms(self.ctx.device))
+        return (self.activation == "silu"        # the products' epilogue applies silu only
+                and ops.fused_rows_ok(num_rows, self.ctx.dtype, widths, ops.device_sms(self.ctx.device))
                 and self.w_gate_up.dtype == torch.bfloat16
                 and self.w_down.dtype == torch.bfloat16 and self.hidden_size % 8 == 0
                 and self.intermediate_size % 8 == 0)
@@ -63,10 +72,10 @@ class SwiGLU(FeedForward):
 
     def forward(self, x, inputs, epilogue=None, residual32=None):
         rows = x.x.shape[0] if isinstance(x, ops.NormedRows) else x.shape[0]
-        if self.block == 64 and (self.fusable(rows) or self._gate_up_fuses(rows)):
+        if self.block == 64 and self.activation == "silu" and (self.fusable(rows) or self._gate_up_fuses(rows)):
             h = ops.linear(x, self.w_gate_up, out_dtype=self.ctx.dtype, swiglu=True)
         else:
             gu = ops.linear(x, self.w_gate_up, out_dtype=self.ctx.dtype)
-            h = ops.swiglu(gu, block=self.block)
+            h = ops.swiglu(gu, block=self.block, activation=self.activation)
         return ops.linear(h, self.w_down, out_dtype=self.ctx.dtype, epilogue=epilogue,
                           residual32=residual32 if epilogue is None else None)

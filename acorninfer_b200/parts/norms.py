@@ -1,4 +1,5 @@
-"""RMSNorm: ``x * rsqrt(mean(x^2) + eps) * w`` in float32, one rounding at the end.
+"""RMSNorm: ``x * rsqrt(mean(x^2) + eps) * w`` in float32, one rounding at the end; and LayerNorm with
+weight and bias: ``(x - mean) * rsqrt(var + eps) * w + b``, var the mean of the squared deviations.
 
 Reference: ``RMSNorm`` in ``acorninfer/models/qwen3.py:50-60`` (the weight multiplies in
 float32 before the cast) and the fused residual-add form in ``acorninfer/ops/rmsnorm.py:15-36``.
@@ -48,3 +49,37 @@ class RMSNorm(Norm):
 
     def add_forward(self, resid32, delta, out=None, rows=None):
         return ops.add_rmsnorm(resid32, delta, self.weight32, self.eps, self.ctx.dtype, row_idx=rows, out=out)
+
+
+@NORMS.register("layernorm")
+class LayerNorm(Norm):
+    """``(x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * w + b`` in float32, one rounding.  ``tensor`` names
+    the weight relative to the part's prefix and ``bias_tensor`` the bias (None: no bias)."""
+
+    graph_safe = True
+    accepts_pair = True           # add_forward takes an ``ops.DeltaPair`` (two results to add) as well
+
+    def __init__(self, ctx: BuildContext, width: int, eps: float, tensor: str = "weight", bias_tensor: str | None = "bias"):
+        self.ctx = ctx
+        self.width = width
+        self.eps = float(eps)
+        self.tensor, self.bias_tensor = tensor, bias_tensor
+        self.weight32: torch.Tensor | None = None
+        self.bias32: torch.Tensor | None = None
+
+    def tensor_specs(self):
+        specs = {self.tensor: TensorSpec((self.width,), "norm")}
+        if self.bias_tensor is not None:
+            specs[self.bias_tensor] = TensorSpec((self.width,), "bias")
+        return specs
+
+    def bind(self, tensors):
+        self.weight32 = tensors[self.tensor].to(torch.float32).contiguous()
+        if self.bias_tensor is not None:
+            self.bias32 = tensors[self.bias_tensor].to(torch.float32).contiguous()
+
+    def forward(self, x32, out=None, rows=None):
+        return ops.add_layernorm(x32, None, self.weight32, self.bias32, self.eps, self.ctx.dtype, row_idx=rows, out=out)
+
+    def add_forward(self, resid32, delta, out=None, rows=None):
+        return ops.add_layernorm(resid32, delta, self.weight32, self.bias32, self.eps, self.ctx.dtype, row_idx=rows, out=out)
