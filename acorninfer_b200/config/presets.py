@@ -1,7 +1,7 @@
 """Sizes of published Qwen3 dense models as ``config.json`` dictionaries, for runs with random
 weights (benchmarks, the random-weights mode): no checkpoint is needed to measure at a model's
 layer sizes.  Only the keys the architecture reads are given.  For Kogonex, of which no model is
-published, two size sets with layers as wide as real models have them."""
+published, two size sets with layers as wide as real models have them; the same for Vagulorn."""
 
 from __future__ import annotations
 
@@ -53,6 +53,33 @@ PRESETS.update({
     "kogonex-w2048": _kogonex(2048, 65536, heads=16, dim=128, rot=64, vdim=128, rank=384, window=1024, d_heads=16,
                               d_kv_heads=8, d_dim=128, d_vdim=128, taps=4, decay_rank=64, gate_rank=128, ff=1024, experts=30,
                               identity=2, top=6, groups=4, keep=2),
+})
+
+
+def _vagulorn(width: int, vocab: int, heads: int, kv_heads: int, ff: int, span: int, ssm_heads: int, ssm_groups: int,
+              repeats: int = 2) -> dict:
+    """Layers in the pattern state space, attention in blocks, attention beside linear attention, state space,
+    ``repeats`` times; heads of 128, a state of 128 per state-space head of 64 inputs."""
+    mlp = {"kind": "dense", "ff": ff}
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+           "rot": {"base": 1e6, "dims": 64}}
+    ssm = {"heads": ssm_heads, "vdim": 64, "state": 128, "groups": ssm_groups, "conv": 4, "norm_groups": ssm_groups}
+    decay = [1.0 - 2.0 ** -(5 + 3 * h / max(1, heads - 1)) for h in range(heads)]
+    layers = []
+    for _ in range(repeats):
+        layers.append({"type": "mamba2", "mixer": dict(ssm), "mlp": mlp})
+        layers.append({"type": "attention", "mixer": dict(att, mask={"size": span}), "mlp": mlp})
+        layers.append({"type": "parallel", "mlp": mlp, "mixer": {
+            "left": dict(att, mask={"size": span, "keep_first": 4}), "left_scale": 0.8,
+            "right": {"heads": heads, "dim": 128, "vdim": 128, "decay": decay}, "right_scale": 0.9}})
+        layers.append({"type": "mamba2", "mixer": dict(ssm), "mlp": mlp})
+    return {"architecture": "Vagulorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 32.0},
+            "layers": layers}
+
+
+PRESETS.update({
+    "vagulorn-w1024": _vagulorn(1024, 32768, heads=8, kv_heads=2, ff=3072, span=1024, ssm_heads=32, ssm_groups=4),
+    "vagulorn-w2048": _vagulorn(2048, 65536, heads=16, kv_heads=4, ff=6144, span=1024, ssm_heads=64, ssm_groups=8),
 })
 
 

@@ -13,7 +13,7 @@ the cache of the live requests) with the measured copy bandwidth.  Weights are r
 (seeded N(0, 0.02), norms 1), token ids uniform random: synthetic data.  Weights
 (15 GB) are far larger than L2, so no L2 flush is needed between steps.
 
-``--design kogonex`` is another workload and prints another line: prefill and decode of the Kogonex
+``--design kogonex`` (or ``vagulorn``) is another workload and prints another line: prefill and decode of that
 architecture at two sets of layer sizes beside Qwen3 dense of equal width, depth, vocabulary and active
 feed-forward width, with the device time of every kernel of one prefill and one decode step.
 """
@@ -581,13 +581,35 @@ def reference_arm(args) -> int:
 
 # ------------------------------------------------------------------ Kogonex beside Qwen3 at equal size
 
-KOGONEX_SIZES = ("w1024", "w2048")        # presets "kogonex-<name>" of acorninfer_b200/config/presets.py
+KOGONEX_SIZES = ("w1024", "w2048")        # presets "kogonex-<name>", "vagulorn-<name>" of acorninfer_b200/config/presets.py
 
 
 def kogonex_config(name: str):
     from acorninfer_b200.config.presets import preset
     from acorninfer_b200.registry import config_from_dict
     return config_from_dict(preset(f"kogonex-{name}"))
+
+
+def design_models(design: str, name: str) -> dict:
+    """The design at the size set ``name`` and Qwen3 dense of the same width, depth, vocabulary and (active)
+    feed-forward width."""
+    from acorninfer_b200.config.model_config import Qwen3Config
+    from acorninfer_b200.config.presets import preset
+    from acorninfer_b200.registry import config_from_dict
+    if design == "kogonex":
+        cfg = kogonex_config(name)
+        latent = next(l.mixer for l in cfg.layers if hasattr(l.mixer, "kv_rank"))
+        moe = cfg.layers[0].mlp
+        heads, kv_heads, ff = latent.heads, max(1, latent.heads // 4), moe.top * moe.ff
+    else:
+        cfg = config_from_dict(preset(f"{design}-{name}"))
+        att = next(l.mixer for l in cfg.layers if l.type == "attention")
+        heads, kv_heads, ff = att.heads, att.kv_heads, cfg.layers[0].ff
+    return {design: cfg,
+            "qwen3": Qwen3Config(num_hidden_layers=len(cfg.layers), hidden_size=cfg.hidden_size, num_attention_heads=heads,
+                                 num_key_value_heads=kv_heads, head_dim=128, intermediate_size=ff, rms_norm_eps=1e-6,
+                                 rope_theta=1e6, vocab_size=cfg.vocab_size, tie_word_embeddings=False, bos_token_id=None,
+                                 eos_token_id=())}
 
 
 def kernel_times(runner, entries_fn, torch) -> dict:
@@ -616,30 +638,21 @@ def kernel_times(runner, entries_fn, torch) -> dict:
 
 
 def design_bench(args) -> int:
-    """``--design kogonex``: prefill and decode of Kogonex at layer sizes of a real model (random weights), beside
-    Qwen3 dense of the same width, depth, vocabulary and active feed-forward width."""
+    """``--design kogonex|vagulorn``: prefill and decode of the design at layer sizes of a real model (random
+    weights), beside Qwen3 dense of the same width, depth, vocabulary and active feed-forward width."""
     import torch
 
-    from acorninfer_b200.config.model_config import Qwen3Config
     from acorninfer_b200.engine.batch import StepEntry
     from acorninfer_b200.engine.runner import ModelRunner
 
     pk = peaks()
-    out = {"metric": "Kogonex beside Qwen3 dense at equal width, depth and active feed-forward width (1 B200)",
+    design = args.design
+    out = {"metric": f"{design.capitalize()} beside Qwen3 dense at equal width, depth and active feed-forward width (1 B200)",
            "unit": "tokens/s", "dtype": "bf16", "data": "synthetic", "impl": "ours", "n_gpus": 1, "steps": args.steps,
            "warmup": args.warmup, "peaks": pk, "sizes": {}}
     context, prompt = 2048, 2048
     for name in (args.design_sizes.split(",") if args.design_sizes else list(KOGONEX_SIZES)):
-        kcfg = kogonex_config(name)
-        latent = next(l.mixer for l in kcfg.layers if hasattr(l.mixer, "kv_rank"))
-        moe = kcfg.layers[0].mlp
-        models = {
-            "kogonex": kcfg,
-            "qwen3": Qwen3Config(num_hidden_layers=len(kcfg.layers), hidden_size=kcfg.hidden_size,
-                                 num_attention_heads=latent.heads, num_key_value_heads=max(1, latent.heads // 4), head_dim=128,
-                                 intermediate_size=moe.top * moe.ff, rms_norm_eps=1e-6, rope_theta=1e6,
-                                 vocab_size=kcfg.vocab_size, tie_word_embeddings=False, bos_token_id=None, eos_token_id=()),
-        }
+        models = design_models(design, name)
         res = {}
         for which, cfg in models.items():
             max_b = 64
@@ -648,6 +661,8 @@ def design_bench(args) -> int:
                                              max_requests=max_b + 2, max_step_tokens=4096)
             for g in runner.manager.groups:
                 g.storage.normal_(0, 1)
+                if g.value_storage is not None:
+                    g.value_storage.normal_(0, 1)
             r = {"prefill_ms": round(time_prefill(runner, prompt, 4, torch), 3)}
             r["prefill_tok_s"] = round(prompt / (r["prefill_ms"] / 1e3), 1)
             for b in (1, 8, 64):
@@ -675,7 +690,7 @@ def design_bench(args) -> int:
             gc.collect()
             torch.cuda.empty_cache()
         out["sizes"][name] = res
-    out["value"] = out["sizes"][next(iter(out["sizes"]))]["kogonex"]["decode_b8_tok_s"]
+    out["value"] = out["sizes"][next(iter(out["sizes"]))][design]["decode_b8_tok_s"]
     print(json.dumps(out))
     return 0
 
@@ -706,7 +721,7 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="only the batch of the headline value")
     ap.add_argument("--skip-extra", action="store_true",
                     help="leave out the per-kernel table, the continuous-batching, long-context and float32 runs")
-    ap.add_argument("--design", default=None, choices=["kogonex"],
+    ap.add_argument("--design", default=None, choices=["kogonex", "vagulorn"],
                     help="another workload: this design at layer sizes of a real model beside Qwen3 dense at equal size")
     ap.add_argument("--design-sizes", default=None, help="with --design: comma-separated names of the size sets to run")
     args = ap.parse_args()
