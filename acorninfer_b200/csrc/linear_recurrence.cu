@@ -19,8 +19,9 @@
 //                   before the norm (y silu(z)) or after it (sigmoid(z)); one rounding
 //
 // The columns of S (one per element of x) never mix, so a block of linear_scan takes a row, a head and
-// a tile of columns; a column's N state entries are spread over LN lanes (N <= 16 LN), entry n with
-// lane n % LN, and y's sum over n ends with shuffles among those lanes.  The tokens' a, w, b, c, x come
+// a tile of columns; a column's N state entries are spread over LN lanes (N <= 16 LN) in runs of four
+// (entry n with lane (n / 4) % LN, so that a lane reads its keys 16 bytes at a time; a token's keys are
+// padded with zeros to 16 LN in shared memory), and y's sum over n ends with shuffles among those lanes.  The tokens' a, w, b, c, x come
 // through shared memory eight tokens at a time.  In the state slot S lies as [H, V, N].
 #include "common.cuh"
 
@@ -110,92 +111,206 @@ struct ScanParams {
     const int* row_start;
     const int* row_slot;
     int H, G, N, V, LN;
+    // long rows in segments of `seg` tokens (SCAN_SEGMENTS / SCAN_FINISH): per row nseg + 1 states
+    // [H, V, N] (the row's state before the step, then the state each segment but the last ends with when it
+    // starts from nothing; segment 0 starts from the row's state) and the segments' products of decays [nseg, H]
+    float* seg_state;
+    float* seg_decay;
+    int seg, nseg;
 };
 
+#define SCAN_WHOLE 0        // a row from its slot's state to the end, the state back into the slot
+#define SCAN_SEGMENTS 1     // every segment but a row's last: its end state and the product of its decays
+#define SCAN_FINISH 2       // every segment from the state it really starts with: y, and the row's last state
+
+__device__ __forceinline__ void scan_cp4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src));
+}
+
+// A recurrence runs over a row's tokens one after the other; what runs side by side is heads, columns
+// and rows.  A prompt of thousands of tokens alone in its step would leave most of the device idle, so
+// long rows are cut into segments that run side by side in two passes: SCAN_SEGMENTS takes every segment
+// from a zero state (the first from the row's state) to the state it ends with; SCAN_FINISH puts the
+// states before its segment together (S <- P_j S + E_j over the earlier segments: the recurrence is
+// linear in S), runs the segment again from there and writes y.  Twice the arithmetic, nseg times the
+// blocks.  The tokens' a, w, b, c, x are staged by cp.async, one stage ahead of the arithmetic.
+template <int MODE>
 __global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(const ScanParams p) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     const int cpb = SCAN_THREADS / p.LN;                // columns a block takes
-    float* sB = sm;                                     // [SCAN_TOKENS][N]
-    float* sC = sB + SCAN_TOKENS * p.N;
-    float* sX = sC + SCAN_TOKENS * p.N;                 // [SCAN_TOKENS][cpb]
-    float* sA = sX + SCAN_TOKENS * cpb;                 // [SCAN_TOKENS]
-    float* sW = sA + SCAN_TOKENS;
+    const int NS = SCAN_STRIP * p.LN;                   // a token's keys in shared memory: N of them, then zeros
+    const int stage_floats = SCAN_TOKENS * (2 * NS + cpb + 2);
+    for (int i = threadIdx.x; i < 2 * stage_floats; i += SCAN_THREADS) sm[i] = 0.f;
+    __syncthreads();
     pdl_wait();
     pdl_trigger();
-    const int h = blockIdx.y, r = blockIdx.z;
+    const int h = blockIdx.y;
+    const int r = MODE == SCAN_WHOLE ? blockIdx.z : blockIdx.z / p.nseg;
+    const int sg = MODE == SCAN_WHOLE ? 0 : blockIdx.z % p.nseg;
     const int g = h / (p.H / p.G);
     const int col = threadIdx.x / p.LN, l = threadIdx.x % p.LN;
     const int v0 = blockIdx.x * cpb, v = v0 + col;
     const bool live = v < p.V;
-    const int first = p.row_start[r], L = p.row_start[r + 1] - first;
-    float* S = p.state + (int64_t)p.row_slot[r] * p.slot_stride + p.state_off + ((int64_t)h * p.V + (live ? v : 0)) * p.N;
+    int first = p.row_start[r], L = p.row_start[r + 1] - first;
+    int nseg_r = 1;
+    if (MODE != SCAN_WHOLE) {
+        nseg_r = (L + p.seg - 1) / p.seg;
+        if (sg >= nseg_r || (MODE == SCAN_SEGMENTS && sg == nseg_r - 1 && sg > 0)) return;
+        first += sg * p.seg;
+        L = min(p.seg, L - sg * p.seg);
+    }
+    const int64_t strip = ((int64_t)h * p.V + (live ? v : 0)) * p.N;
+    float* S = p.state + (int64_t)p.row_slot[r] * p.slot_stride + p.state_off + strip;
+    const int64_t HVN = (int64_t)p.H * p.V * p.N;
+    float* seg_states = MODE == SCAN_WHOLE ? nullptr : p.seg_state + (int64_t)r * (p.nseg + 1) * HVN + strip;
     float s[SCAN_STRIP];
 #pragma unroll
     for (int i = 0; i < SCAN_STRIP; ++i) {
-        const int n = l + p.LN * i;
-        s[i] = (live && n < p.N) ? S[n] : 0.f;
+        const int n = (i >> 2) * 4 * p.LN + 4 * l + (i & 3);
+        const bool ok = live && n < p.N;
+        if (MODE == SCAN_WHOLE) {
+            s[i] = ok ? S[n] : 0.f;
+        } else if (MODE == SCAN_SEGMENTS) {
+            s[i] = (ok && sg == 0) ? S[n] : 0.f;
+            if (ok && sg == 0) seg_states[n] = s[i];            // the row's state before the step
+        } else {
+            s[i] = ok ? seg_states[(sg == 0 ? 0 : HVN) + n] : 0.f;
+        }
+    }
+    if (MODE == SCAN_SEGMENTS && sg == nseg_r - 1) return;      // a row of one segment: only its state was copied
+    if (MODE == SCAN_FINISH) {
+        for (int j = 1; j < sg; ++j) {                          // the states the earlier segments end with, folded
+            const float pj = p.seg_decay[((int64_t)r * p.nseg + j) * p.H + h];
+#pragma unroll
+            for (int i = 0; i < SCAN_STRIP; ++i) {
+                const int n = (i >> 2) * 4 * p.LN + 4 * l + (i & 3);
+                if (live && n < p.N) s[i] = fmaf(pj, s[i], seg_states[(int64_t)(j + 1) * HVN + n]);
+            }
+        }
     }
     const float skip = p.skip ? p.skip[h] : 0.f;
-    for (int t0 = 0; t0 < L; t0 += SCAN_TOKENS) {
+    float prod = 1.f;
+    auto stage_in = [&](int t0, int stage) {
+        float* sB = sm + stage * stage_floats;                  // [SCAN_TOKENS][NS]
+        float* sC = sB + SCAN_TOKENS * NS;
+        float* sX = sC + SCAN_TOKENS * NS;                      // [SCAN_TOKENS][cpb]
+        float* sA = sX + SCAN_TOKENS * cpb;                     // [SCAN_TOKENS]
+        float* sW = sA + SCAN_TOKENS;
         const int nt = min(SCAN_TOKENS, L - t0);
+        if (nt > 0) {
+            for (int tt = 0; tt < nt; ++tt) {
+                const int64_t tok = first + t0 + tt;
+                for (int n = threadIdx.x; n < p.N; n += SCAN_THREADS) {
+                    scan_cp4(sB + tt * NS + n, p.b + tok * p.ldb + (int64_t)g * p.N + n);
+                    if (MODE != SCAN_SEGMENTS) scan_cp4(sC + tt * NS + n, p.c + tok * p.ldc + (int64_t)g * p.N + n);
+                }
+            }
+            for (int i = threadIdx.x; i < nt * cpb; i += SCAN_THREADS) {
+                const int tt = i / cpb, cc = i - tt * cpb;
+                if (v0 + cc < p.V) scan_cp4(sX + i, p.x + (int64_t)(first + t0 + tt) * p.ldx + (int64_t)h * p.V + v0 + cc);
+                else sX[i] = 0.f;
+            }
+            if (threadIdx.x < nt) {
+                const int64_t tok = first + t0 + threadIdx.x;
+                scan_cp4(sA + threadIdx.x, p.lda ? p.decay + tok * p.lda + h : p.decay + h);
+                if (p.w) scan_cp4(sW + threadIdx.x, p.w + tok * p.ldw + h);
+                else sW[threadIdx.x] = 1.f;
+            }
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+    stage_in(0, 0);
+    for (int t0 = 0, it = 0; t0 < L; t0 += SCAN_TOKENS, ++it) {
+        const int stage = it & 1;
+        stage_in(t0 + SCAN_TOKENS, stage ^ 1);                  // the stage the step before finished with
+        asm volatile("cp.async.wait_group 1;\n" ::);
         __syncthreads();
-        for (int i = threadIdx.x; i < nt * p.N; i += SCAN_THREADS) {
-            const int tt = i / p.N, n = i - tt * p.N;
-            const int64_t tok = first + t0 + tt;
-            sB[tt * p.N + n] = p.b[tok * p.ldb + (int64_t)g * p.N + n];
-            sC[tt * p.N + n] = p.c[tok * p.ldc + (int64_t)g * p.N + n];
-        }
-        for (int i = threadIdx.x; i < nt * cpb; i += SCAN_THREADS) {
-            const int tt = i / cpb, cc = i - tt * cpb;
-            sX[i] = v0 + cc < p.V ? p.x[(int64_t)(first + t0 + tt) * p.ldx + (int64_t)h * p.V + v0 + cc] : 0.f;
-        }
-        if (threadIdx.x < nt) {
-            const int64_t tok = first + t0 + threadIdx.x;
-            sA[threadIdx.x] = p.lda ? p.decay[tok * p.lda + h] : p.decay[h];
-            sW[threadIdx.x] = p.w ? p.w[tok * p.ldw + h] : 1.f;
-        }
-        __syncthreads();
+        const float* sB = sm + stage * stage_floats;
+        const float* sC = sB + SCAN_TOKENS * NS;
+        const float* sX = sC + SCAN_TOKENS * NS;
+        const float* sA = sX + SCAN_TOKENS * cpb;
+        const float* sW = sA + SCAN_TOKENS;
+        const int nt = min(SCAN_TOKENS, L - t0);
         for (int tt = 0; tt < nt; ++tt) {
             const float a = sA[tt], xv = sX[tt * cpb + col];
             const float u = sW[tt] * xv;
-            const float* bb = sB + tt * p.N;
-            const float* cc = sC + tt * p.N;
+            const float4* bb = reinterpret_cast<const float4*>(sB + tt * NS) + l;
+            const float4* cc = reinterpret_cast<const float4*>(sC + tt * NS) + l;
             float acc = 0.f;
+            // entries beyond N hold zeros and stay zero (their keys are zeros)
 #pragma unroll
-            for (int i = 0; i < SCAN_STRIP; ++i) {
-                const int n = l + p.LN * i;
-                if (n < p.N) {
-                    s[i] = fmaf(a, s[i], bb[n] * u);
-                    acc = fmaf(s[i], cc[n], acc);
+            for (int i4 = 0; i4 < SCAN_STRIP / 4; ++i4) {
+                const float4 b4 = bb[i4 * p.LN];
+                s[4 * i4] = fmaf(a, s[4 * i4], b4.x * u);
+                s[4 * i4 + 1] = fmaf(a, s[4 * i4 + 1], b4.y * u);
+                s[4 * i4 + 2] = fmaf(a, s[4 * i4 + 2], b4.z * u);
+                s[4 * i4 + 3] = fmaf(a, s[4 * i4 + 3], b4.w * u);
+                if (MODE != SCAN_SEGMENTS) {
+                    const float4 c4 = cc[i4 * p.LN];
+                    acc = fmaf(s[4 * i4], c4.x, acc);
+                    acc = fmaf(s[4 * i4 + 1], c4.y, acc);
+                    acc = fmaf(s[4 * i4 + 2], c4.z, acc);
+                    acc = fmaf(s[4 * i4 + 3], c4.w, acc);
                 }
             }
-            for (int o = p.LN >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (live && l == 0) p.y[(int64_t)(first + t0 + tt) * p.H * p.V + (int64_t)h * p.V + v] = acc + skip * xv;
+            if (MODE == SCAN_SEGMENTS) {
+                prod *= a;
+            } else {
+                for (int o = p.LN >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                if (live && l == 0) p.y[(int64_t)(first + t0 + tt) * p.H * p.V + (int64_t)h * p.V + v] = acc + skip * xv;
+            }
         }
+        __syncthreads();                                        // the stage may be filled again
     }
+    asm volatile("cp.async.wait_group 0;\n" ::);
+    if (MODE == SCAN_FINISH && sg != nseg_r - 1) return;        // only a row's last segment ends with the row's state
+    float* dst = MODE == SCAN_SEGMENTS ? seg_states + (int64_t)(sg + 1) * HVN : S;
     if (live) {
 #pragma unroll
         for (int i = 0; i < SCAN_STRIP; ++i) {
-            const int n = l + p.LN * i;
-            if (n < p.N) S[n] = s[i];
+            const int n = (i >> 2) * 4 * p.LN + 4 * l + (i & 3);
+            if (n < p.N) dst[n] = s[i];
         }
     }
+    if (MODE == SCAN_SEGMENTS && blockIdx.x == 0 && threadIdx.x == 0)
+        p.seg_decay[((int64_t)r * p.nseg + sg) * p.H + h] = prod;
 }
 
+// seg_tokens = 0: every row in one piece (seg_state, seg_decay unused).  Otherwise rows are cut into segments of
+// seg_tokens tokens, at most nseg a row (the caller sees to nseg * seg_tokens >= the longest row); seg_state holds
+// rows * (nseg + 1) * H * V * N floats, seg_decay rows * nseg * H.
 extern "C" int acorn_linear_scan(const float* b, int64_t ldb, const float* c, int64_t ldc, const float* x, int64_t ldx,
                                  const float* decay, int64_t lda, const float* w, int64_t ldw, const float* skip,
                                  float* state, int64_t slot_stride, int64_t state_off, float* y, const int* row_start,
-                                 const int* row_slot, int rows, int H, int G, int N, int V, cudaStream_t stream) {
+                                 const int* row_slot, int rows, int H, int G, int N, int V, int seg_tokens, int nseg,
+                                 float* seg_state, float* seg_decay, cudaStream_t stream) {
     if (rows <= 0) return 0;
-    if (H < 1 || G < 1 || H % G || N < 1 || N > 32 * SCAN_STRIP || V < 1 || rows > 65535 || H > 65535)
-        return ACORN_ERR_UNSUPPORTED;
+    if (H < 1 || G < 1 || H % G || N < 1 || N > 32 * SCAN_STRIP || V < 1 || H > 65535) return ACORN_ERR_UNSUPPORTED;
+    const bool cut = seg_tokens > 0;
+    if (cut && (nseg < 2 || seg_state == nullptr || seg_decay == nullptr)) return ACORN_ERR_UNSUPPORTED;
+    if ((int64_t)rows * (cut ? nseg : 1) > 65535) return ACORN_ERR_UNSUPPORTED;
     int LN = 1;
     while (LN * SCAN_STRIP < N) LN *= 2;
     const int cpb = SCAN_THREADS / LN;
     ScanParams p = {b, ldb, c, ldc, x, ldx, decay, lda, w, ldw, skip, state, slot_stride, state_off, y, row_start, row_slot,
-                    H, G, N, V, LN};
-    const size_t smem = (size_t)SCAN_TOKENS * (2 * N + cpb + 2) * sizeof(float);
-    return acorn_launch(linear_scan_kernel, dim3((V + cpb - 1) / cpb, H, rows), dim3(SCAN_THREADS), smem, stream, p);
+                    H, G, N, V, LN, seg_state, seg_decay, seg_tokens, cut ? nseg : 1};
+    const size_t smem = (size_t)2 * SCAN_TOKENS * (2 * SCAN_STRIP * LN + cpb + 2) * sizeof(float);
+    if (smem > 48 * 1024) {
+        static AcornPerDevice configured;
+        if (!configured.seen()) {
+            const int most = (int)((size_t)2 * SCAN_TOKENS * (2 * 32 * SCAN_STRIP + 4 + 2) * sizeof(float));
+            cudaError_t e = cudaFuncSetAttribute(linear_scan_kernel<SCAN_WHOLE>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(linear_scan_kernel<SCAN_SEGMENTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(linear_scan_kernel<SCAN_FINISH>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+            if (e != cudaSuccess) return (int)e;
+            configured.mark();
+        }
+    }
+    const dim3 grid((V + cpb - 1) / cpb, H, rows * (cut ? nseg : 1));
+    if (!cut) return acorn_launch(linear_scan_kernel<SCAN_WHOLE>, grid, dim3(SCAN_THREADS), smem, stream, p);
+    const int rc = acorn_launch(linear_scan_kernel<SCAN_SEGMENTS>, grid, dim3(SCAN_THREADS), smem, stream, p);
+    if (rc != 0) return rc;
+    return acorn_launch(linear_scan_kernel<SCAN_FINISH>, grid, dim3(SCAN_THREADS), smem, stream, p);
 }
 
 // y32 [T, W] in `groups` equal parts.  mode 0: u = y silu(z), out = u / rms_part(u) * weight;

@@ -101,7 +101,7 @@ class _Sigs:
     acorn_silu_rows = [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_void_p]
     acorn_linear_scan = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
                          c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                         c_int, c_void_p]
+                         c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]
     acorn_gated_norm = [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_float, c_int,
                         c_float, c_int, c_void_p]
     acorn_cast = [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
@@ -1351,13 +1351,36 @@ def silu_rows(x: torch.Tensor) -> torch.Tensor:
     return out
 
 
+SCAN_MIN_SEGMENT = 64             # tokens: shorter segments are not worth a second pass
+SCAN_MAX_SEGMENTS = 16
+SCAN_ENOUGH_BLOCKS = 2400         # blocks of 128 threads that fill the device (148 SMs, 16 a piece)
+SCAN_SCRATCH_BYTES = 1 << 30
+
+
+def scan_segments(longest_row: int, num_rows: int, heads: int, n: int, v: int) -> tuple[int, int]:
+    """(tokens a segment, segments a row) for ``linear_scan``, (0, 1) for rows in one piece.  Rows run
+    side by side with heads and tiles of columns; where those are too few to fill the device and a row is
+    long, rows are cut into segments that run side by side (at the price of a second pass)."""
+    lanes = 1
+    while lanes * 16 < n:
+        lanes *= 2
+    blocks = num_rows * heads * -(-v // (128 // lanes))
+    nseg = min(SCAN_MAX_SEGMENTS, longest_row // SCAN_MIN_SEGMENT, -(-SCAN_ENOUGH_BLOCKS // blocks), 65535 // max(1, num_rows),
+               SCAN_SCRATCH_BYTES // (4 * num_rows * heads * n * v) - 1)
+    if nseg < 2:
+        return 0, 1
+    return -(-longest_row // nseg), nseg
+
+
 def linear_scan(b: torch.Tensor, c: torch.Tensor, x: torch.Tensor, decay: torch.Tensor, w: torch.Tensor | None,
                 skip32: torch.Tensor | None, state: torch.Tensor, state_off: int, row_start: torch.Tensor,
-                row_slot: torch.Tensor, num_rows: int, heads: int, groups: int, n: int, v: int) -> torch.Tensor:
+                row_slot: torch.Tensor, num_rows: int, heads: int, groups: int, n: int, v: int,
+                longest_row: int = 1) -> torch.Tensor:
     """Per head ``S <- a S + b (w x)^T; y = S^T c + skip x`` over every row's tokens, from the state in the
     row's slot (``[heads, v, n]`` float32 at ``state_off``, updated in place).  ``b``, ``c`` [T, groups * n],
     ``x`` [T, heads * v] float32 (column slices allowed); ``decay`` [T, heads] per token or [heads] for all;
-    ``w`` [T, heads] or None.  Returns float32 y [T, heads * v]."""
+    ``w`` [T, heads] or None.  Returns float32 y [T, heads * v].  ``longest_row``: a bound on the tokens of a row
+    (a host number); long rows of a step with few rows are run in segments side by side (``scan_segments``)."""
     for t, name in ((b, "b"), (c, "c"), (x, "x")):
         _rows2(t, name, torch.float32)
     _check(state, "state", torch.float32, 2)
@@ -1375,11 +1398,16 @@ def linear_scan(b: torch.Tensor, c: torch.Tensor, x: torch.Tensor, decay: torch.
     if skip32 is not None:
         _check(skip32, "skip", torch.float32, 1)
     y = torch.empty((T, heads * v), dtype=torch.float32, device=x.device)
+    seg, nseg = scan_segments(int(longest_row), num_rows, heads, n, v)
+    seg_state = seg_decay = None
+    if seg:
+        seg_state = torch.empty((num_rows, nseg + 1, heads * n * v), dtype=torch.float32, device=x.device)
+        seg_decay = torch.empty((num_rows, nseg, heads), dtype=torch.float32, device=x.device)
     _ok(lib().acorn_linear_scan(b.data_ptr(), b.stride(0), c.data_ptr(), c.stride(0), x.data_ptr(), x.stride(0),
                                 decay.data_ptr(), decay.stride(0) if decay.dim() == 2 else 0, _ptr(w),
                                 w.stride(0) if w is not None else 0, _ptr(skip32), state.data_ptr(), state.stride(0),
                                 int(state_off), y.data_ptr(), row_start.data_ptr(), row_slot.data_ptr(), num_rows, heads,
-                                groups, n, v, _stream()), "linear_scan")
+                                groups, n, v, seg, nseg, _ptr(seg_state), _ptr(seg_decay), _stream()), "linear_scan")
     return y
 
 

@@ -31,7 +31,9 @@ from .base import MIXERS, BuildContext, CacheNeeds, Mixer, StateNeeds, TensorSpe
 
 class _RecurrentMixer(Mixer):
     """Common to both: the state is one float32 vector per request, S of all heads first, addressed from
-    ``state_base`` (a mixer that shares a request's slot with another gets its part of the vector)."""
+    ``state_base`` (a mixer that shares a request's slot with another gets its part of the vector).
+    The one host-side value of the step they read is its longest row (long rows are run in segments); it is 1
+    in every step of single tokens, the only steps of a model with state that are captured and replayed."""
 
     graph_safe = True
     adds_residual = True
@@ -90,7 +92,7 @@ class StateSpace(_RecurrentMixer):
                               inputs.num_rows, C, self.taps)
         y = ops.linear_scan(act[:, I:I + GN], act[:, I + GN:], act[:, :I], decay, dt, self.d32, cache.state,
                             self.state_base, inputs.row_start, inputs.row_slot, inputs.num_rows, self.H, self.G,
-                            self.N, self.V)
+                            self.N, self.V, longest_row=inputs.plan.max_q_len)
         if out is None:
             out = torch.empty((proj.shape[0], I), dtype=self.ctx.dtype, device=proj.device)
         return ops.gated_norm(y, proj[:, :I], self.norm32, self.eps, self.norm_groups, True, out, out_scale)
@@ -136,7 +138,7 @@ class DecayLinearAttention(_RecurrentMixer):
         act = ops.silu_rows(proj[:, :2 * Hd + Hv])
         y = ops.linear_scan(act[:, Hd:2 * Hd], act[:, :Hd], act[:, 2 * Hd:], self._decay32, None, None, cache.state,
                             self.state_base, inputs.row_start, inputs.row_slot, inputs.num_rows, self.H, self.H,
-                            self.dim, self.V)
+                            self.dim, self.V, longest_row=inputs.plan.max_q_len)
         if out is None:
             out = torch.empty((proj.shape[0], Hv), dtype=self.ctx.dtype, device=proj.device)
         return ops.gated_norm(y, proj[:, 2 * Hd + Hv:], self.norm32, self.eps, 1, False, out, out_scale)

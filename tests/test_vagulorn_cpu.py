@@ -131,3 +131,13 @@ def test_plain_model_is_causal_and_sensitive_to_far_tokens(tmp_path):
     b = plain.forward(tiny["cfg"].to_dict(), w, other)
     assert (a[:30] - b[:30]).abs().max() == 0 and (a[30] - b[30]).abs().max() > 1e-3
     assert (a[215] - b[215]).abs().max() > 1e-9
+
+
+def test_long_rows_are_cut_into_segments_only_where_the_device_is_not_full():
+    from acorninfer_b200.kernels.ops import SCAN_MAX_SEGMENTS, SCAN_MIN_SEGMENT, scan_segments
+    assert scan_segments(1, 64, 32, 128, 64) == (0, 1) and scan_segments(100, 1, 32, 128, 64) == (0, 1)
+    seg, nseg = scan_segments(2048, 1, 32, 128, 64)
+    assert 2 <= nseg <= SCAN_MAX_SEGMENTS and seg >= SCAN_MIN_SEGMENT and seg * nseg >= 2048
+    assert scan_segments(2048, 64, 32, 128, 64) == (0, 1)            # 64 rows of 32 heads fill the device themselves
+    seg, nseg = scan_segments(130, 1, 2, 16, 16)
+    assert nseg == 2 and seg == 65

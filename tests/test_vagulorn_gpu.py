@@ -352,20 +352,25 @@ def test_attention_in_blocks_of_positions(dtype, tol, kernel, d, dv, nq, nkv):
     assert (got - want).abs().max() < tol
 
 
+@pytest.mark.parametrize("long", [False, True])
 @pytest.mark.parametrize("H,G,N,V", [(4, 2, 7, 10), (1, 1, 70, 20), (3, 3, 300, 3), (2, 1, 16, 130), (6, 6, 32, 32)])
-def test_linear_scan_carries_state_across_steps_and_slots(H, G, N, V):
+def test_linear_scan_carries_state_across_steps_and_slots(H, G, N, V, long):
     """The recurrence over rows of unequal length from states in scattered slots, in two steps (the second
-    continues the first), against the loop; a slot that is zeroed starts over."""
+    continues the first), against the loop; a slot that is zeroed starts over.  ``long``: rows of hundreds of
+    tokens, which are run in segments side by side (rows shorter than a segment, and of one token, beside them)."""
     o = ops()
     g = torch.Generator().manual_seed(N)
-    slots, lens1, lens2 = [3, 0, 5], [9, 1, 17], [1, 12, 2]
+    slots, lens1, lens2 = ([3, 0, 5], [700, 1, 130], [3, 400, 64]) if long else ([3, 0, 5], [9, 1, 17], [1, 12, 2])
+    if long:
+        assert o.scan_segments(700, 3, H, N, V)[1] >= 4
     state = torch.zeros(7, H * N * V + 11, device=DEV)
     state[:, :] = 123.0                       # what lies in a slot before its request starts must not matter ...
     state[slots] = 0                          # ... once the slot is zeroed
     seqs = []
     for n1, n2 in zip(lens1, lens2):
         T = n1 + n2
-        seqs.append(dict(a=torch.rand(T, H, generator=g).double() * 0.5 + 0.5, dt=torch.rand(T, H, generator=g).double(),
+        seqs.append(dict(a=torch.rand(T, H, generator=g).double() * (0.1 if long else 0.5) + (0.9 if long else 0.5),
+                         dt=torch.rand(T, H, generator=g).double(),
                          B=torch.randn(T, G, N, generator=g).double(), C=torch.randn(T, G, N, generator=g).double(),
                          x=torch.randn(T, H, V, generator=g).double(), D=torch.randn(H, generator=g).double()))
     D = seqs[0]["D"]
@@ -380,7 +385,7 @@ def test_linear_scan_carries_state_across_steps_and_slots(H, G, N, V):
         bc = torch.cat([cat("B", (T, G * N)), cat("C", (T, G * N))], dim=1).contiguous()
         y = o.linear_scan(bc[:, :G * N], bc[:, G * N:], cat("x", (T, H * V)), cat("a", (T, H)), cat("dt", (T, H)),
                           D.float().to(DEV), state, 5, torch.tensor(np.cumsum([0] + lens), **i32),
-                          torch.tensor(slots, **i32), 3, H, G, N, V).cpu().double().view(T, H, V)
+                          torch.tensor(slots, **i32), 3, H, G, N, V, longest_row=max(lens)).cpu().double().view(T, H, V)
         t0 = 0
         for r, n in enumerate(lens):
             ref = want[r][at[r]:at[r] + n]
