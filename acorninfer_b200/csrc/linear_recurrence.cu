@@ -134,10 +134,11 @@ __device__ __forceinline__ void scan_cp4(float* dst, const float* src) {
 // states before its segment together (S <- P_j S + E_j over the earlier segments: the recurrence is
 // linear in S), runs the segment again from there and writes y.  Twice the arithmetic, nseg times the
 // blocks.  The tokens' a, w, b, c, x are staged by cp.async, one stage ahead of the arithmetic.
-template <int MODE>
-__global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(const ScanParams p) {
+template <int MODE, int CPT>
+__global__ void __launch_bounds__(SCAN_THREADS, CPT == 4 ? 3 : 4) linear_scan_kernel(const ScanParams p) {
     extern __shared__ __align__(16) float sm[];
-    const int cpb = SCAN_THREADS / p.LN;                // columns a block takes
+    const int cpl = SCAN_THREADS / p.LN;                // columns side by side in a block; a thread holds CPT of them,
+    const int cpb = cpl * CPT;                          // cpl apart, so a block takes cpb columns
     const int NS = SCAN_STRIP * p.LN;                   // a token's keys in shared memory: N of them, then zeros
     const int stage_floats = SCAN_TOKENS * (2 * NS + cpb + 2);
     for (int i = threadIdx.x; i < 2 * stage_floats; i += SCAN_THREADS) sm[i] = 0.f;
@@ -149,8 +150,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(const ScanPar
     const int sg = MODE == SCAN_WHOLE ? 0 : blockIdx.z % p.nseg;
     const int g = h / (p.H / p.G);
     const int col = threadIdx.x / p.LN, l = threadIdx.x % p.LN;
-    const int v0 = blockIdx.x * cpb, v = v0 + col;
-    const bool live = v < p.V;
+    const int v0 = blockIdx.x * cpb;
     int first = p.row_start[r], L = p.row_start[r + 1] - first;
     int nseg_r = 1;
     if (MODE != SCAN_WHOLE) {
@@ -159,33 +159,41 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(const ScanPar
         first += sg * p.seg;
         L = min(p.seg, L - sg * p.seg);
     }
-    const int64_t strip = ((int64_t)h * p.V + (live ? v : 0)) * p.N;
-    float* S = p.state + (int64_t)p.row_slot[r] * p.slot_stride + p.state_off + strip;
     const int64_t HVN = (int64_t)p.H * p.V * p.N;
-    float* seg_states = MODE == SCAN_WHOLE ? nullptr : p.seg_state + (int64_t)r * (p.nseg + 1) * HVN + strip;
-    float s[SCAN_STRIP];
+    float* slot = p.state + (int64_t)p.row_slot[r] * p.slot_stride + p.state_off;
+    float* seg_states = MODE == SCAN_WHOLE ? nullptr : p.seg_state + (int64_t)r * (p.nseg + 1) * HVN;
+    // column j of the thread is v0 + col + j * cpl; its state entries start at strip0 + j * strip_step within [H, V, N]
+    const int64_t strip0 = ((int64_t)h * p.V + v0 + col) * p.N, strip_step = (int64_t)cpl * p.N;
+    float s[CPT][SCAN_STRIP];
+#define SCAN_LIVE(j) (v0 + col + (j) * cpl < p.V)
+#define SCAN_AT(j) (strip0 + (j) * strip_step)
 #pragma unroll
-    for (int i = 0; i < SCAN_STRIP; ++i) {
-        const int n = (i >> 2) * 4 * p.LN + 4 * l + (i & 3);
-        const bool ok = live && n < p.N;
-        if (MODE == SCAN_WHOLE) {
-            s[i] = ok ? S[n] : 0.f;
-        } else if (MODE == SCAN_SEGMENTS) {
-            s[i] = (ok && sg == 0) ? S[n] : 0.f;
-            if (ok && sg == 0) seg_states[n] = s[i];            // the row's state before the step
-        } else {
-            s[i] = ok ? seg_states[(sg == 0 ? 0 : HVN) + n] : 0.f;
+    for (int j = 0; j < CPT; ++j) {
+#pragma unroll
+        for (int i = 0; i < SCAN_STRIP; ++i) {
+            const int n = (i >> 2) * 4 * p.LN + 4 * l + (i & 3);
+            const bool ok = SCAN_LIVE(j) && n < p.N;
+            if (MODE == SCAN_WHOLE) {
+                s[j][i] = ok ? slot[SCAN_AT(j) + n] : 0.f;
+            } else if (MODE == SCAN_SEGMENTS) {
+                s[j][i] = (ok && sg == 0) ? slot[SCAN_AT(j) + n] : 0.f;
+                if (ok && sg == 0) seg_states[SCAN_AT(j) + n] = s[j][i];          // the row's state before the step
+            } else {
+                s[j][i] = ok ? seg_states[(sg == 0 ? 0 : HVN) + SCAN_AT(j) + n] : 0.f;
+            }
         }
     }
     if (MODE == SCAN_SEGMENTS && sg == nseg_r - 1) return;      // a row of one segment: only its state was copied
     if (MODE == SCAN_FINISH) {
-        for (int j = 1; j < sg; ++j) {                          // the states the earlier segments end with, folded
-            const float pj = p.seg_decay[((int64_t)r * p.nseg + j) * p.H + h];
+        for (int k = 1; k < sg; ++k) {                          // the states the earlier segments end with, folded
+            const float pk = p.seg_decay[((int64_t)r * p.nseg + k) * p.H + h];
 #pragma unroll
-            for (int i = 0; i < SCAN_STRIP; ++i) {
-                const int n = (i >> 2) * 4 * p.LN + 4 * l + (i & 3);
-                if (live && n < p.N) s[i] = fmaf(pj, s[i], seg_states[(int64_t)(j + 1) * HVN + n]);
-            }
+            for (int j = 0; j < CPT; ++j)
+#pragma unroll
+                for (int i = 0; i < SCAN_STRIP; ++i) {
+                    const int n = (i >> 2) * 4 * p.LN + 4 * l + (i & 3);
+                    if (SCAN_LIVE(j) && n < p.N) s[j][i] = fmaf(pk, s[j][i], seg_states[(int64_t)(k + 1) * HVN + SCAN_AT(j) + n]);
+                }
         }
     }
     const float skip = p.skip ? p.skip[h] : 0.f;
@@ -204,11 +212,10 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(const ScanPar
                     scan_cp4(sB + tt * NS + n, p.b + tok * p.ldb + (int64_t)g * p.N + n);
                     if (MODE != SCAN_SEGMENTS) scan_cp4(sC + tt * NS + n, p.c + tok * p.ldc + (int64_t)g * p.N + n);
                 }
-            }
-            for (int i = threadIdx.x; i < nt * cpb; i += SCAN_THREADS) {
-                const int tt = i / cpb, cc = i - tt * cpb;
-                if (v0 + cc < p.V) scan_cp4(sX + i, p.x + (int64_t)(first + t0 + tt) * p.ldx + (int64_t)h * p.V + v0 + cc);
-                else sX[i] = 0.f;
+                for (int cc = threadIdx.x; cc < cpb; cc += SCAN_THREADS) {
+                    if (v0 + cc < p.V) scan_cp4(sX + tt * cpb + cc, p.x + tok * p.ldx + (int64_t)h * p.V + v0 + cc);
+                    else sX[tt * cpb + cc] = 0.f;
+                }
             }
             if (threadIdx.x < nt) {
                 const int64_t tok = first + t0 + threadIdx.x;
@@ -232,48 +239,101 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(const ScanPar
         const float* sW = sA + SCAN_TOKENS;
         const int nt = min(SCAN_TOKENS, L - t0);
         for (int tt = 0; tt < nt; ++tt) {
-            const float a = sA[tt], xv = sX[tt * cpb + col];
-            const float u = sW[tt] * xv;
+            const float a = sA[tt], wt = sW[tt];
+            float xv[CPT], u[CPT], acc[CPT];
+#pragma unroll
+            for (int j = 0; j < CPT; ++j) {
+                xv[j] = sX[tt * cpb + col + j * cpl];
+                u[j] = wt * xv[j];
+                acc[j] = 0.f;
+            }
             const float4* bb = reinterpret_cast<const float4*>(sB + tt * NS) + l;
             const float4* cc = reinterpret_cast<const float4*>(sC + tt * NS) + l;
-            float acc = 0.f;
-            // entries beyond N hold zeros and stay zero (their keys are zeros)
+            // entries beyond N hold zeros and stay zero (their keys are zeros); a key is read once for the
+            // thread's CPT columns
 #pragma unroll
             for (int i4 = 0; i4 < SCAN_STRIP / 4; ++i4) {
                 const float4 b4 = bb[i4 * p.LN];
-                s[4 * i4] = fmaf(a, s[4 * i4], b4.x * u);
-                s[4 * i4 + 1] = fmaf(a, s[4 * i4 + 1], b4.y * u);
-                s[4 * i4 + 2] = fmaf(a, s[4 * i4 + 2], b4.z * u);
-                s[4 * i4 + 3] = fmaf(a, s[4 * i4 + 3], b4.w * u);
-                if (MODE != SCAN_SEGMENTS) {
-                    const float4 c4 = cc[i4 * p.LN];
-                    acc = fmaf(s[4 * i4], c4.x, acc);
-                    acc = fmaf(s[4 * i4 + 1], c4.y, acc);
-                    acc = fmaf(s[4 * i4 + 2], c4.z, acc);
-                    acc = fmaf(s[4 * i4 + 3], c4.w, acc);
+                float4 c4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (MODE != SCAN_SEGMENTS) c4 = cc[i4 * p.LN];
+#pragma unroll
+                for (int j = 0; j < CPT; ++j) {
+                    s[j][4 * i4] = fmaf(a, s[j][4 * i4], b4.x * u[j]);
+                    s[j][4 * i4 + 1] = fmaf(a, s[j][4 * i4 + 1], b4.y * u[j]);
+                    s[j][4 * i4 + 2] = fmaf(a, s[j][4 * i4 + 2], b4.z * u[j]);
+                    s[j][4 * i4 + 3] = fmaf(a, s[j][4 * i4 + 3], b4.w * u[j]);
+                    if (MODE != SCAN_SEGMENTS) {
+                        acc[j] = fmaf(s[j][4 * i4], c4.x, acc[j]);
+                        acc[j] = fmaf(s[j][4 * i4 + 1], c4.y, acc[j]);
+                        acc[j] = fmaf(s[j][4 * i4 + 2], c4.z, acc[j]);
+                        acc[j] = fmaf(s[j][4 * i4 + 3], c4.w, acc[j]);
+                    }
                 }
             }
             if (MODE == SCAN_SEGMENTS) {
                 prod *= a;
             } else {
-                for (int o = p.LN >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-                if (live && l == 0) p.y[(int64_t)(first + t0 + tt) * p.H * p.V + (int64_t)h * p.V + v] = acc + skip * xv;
+                for (int o = p.LN >> 1; o > 0; o >>= 1) {
+#pragma unroll
+                    for (int j = 0; j < CPT; ++j) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+                }
+                float* yrow = p.y + (int64_t)(first + t0 + tt) * p.H * p.V + (int64_t)h * p.V + v0 + col;
+#pragma unroll
+                for (int j = 0; j < CPT; ++j)
+                    if (SCAN_LIVE(j) && l == 0) yrow[j * cpl] = acc[j] + skip * xv[j];
             }
         }
         __syncthreads();                                        // the stage may be filled again
     }
     asm volatile("cp.async.wait_group 0;\n" ::);
     if (MODE == SCAN_FINISH && sg != nseg_r - 1) return;        // only a row's last segment ends with the row's state
-    float* dst = MODE == SCAN_SEGMENTS ? seg_states + (int64_t)(sg + 1) * HVN : S;
-    if (live) {
+    float* dst = MODE == SCAN_SEGMENTS ? seg_states + (int64_t)(sg + 1) * HVN : slot;
+#pragma unroll
+    for (int j = 0; j < CPT; ++j) {
+        if (!SCAN_LIVE(j)) continue;
 #pragma unroll
         for (int i = 0; i < SCAN_STRIP; ++i) {
             const int n = (i >> 2) * 4 * p.LN + 4 * l + (i & 3);
-            if (n < p.N) dst[n] = s[i];
+            if (n < p.N) dst[SCAN_AT(j) + n] = s[j][i];
         }
     }
     if (MODE == SCAN_SEGMENTS && blockIdx.x == 0 && threadIdx.x == 0)
         p.seg_decay[((int64_t)r * p.nseg + sg) * p.H + h] = prod;
+#undef SCAN_LIVE
+#undef SCAN_AT
+}
+
+template <int CPT>
+static int launch_scan(const ScanParams& p, int rows, bool cut, cudaStream_t stream) {
+    const int cpb = SCAN_THREADS / p.LN * CPT;
+    const size_t smem = (size_t)2 * SCAN_TOKENS * (2 * SCAN_STRIP * p.LN + cpb + 2) * sizeof(float);
+    if (smem > 48 * 1024) {
+        static AcornPerDevice configured;
+        if (!configured.seen()) {
+            const int most = (int)((size_t)2 * SCAN_TOKENS * (2 * 32 * SCAN_STRIP + SCAN_THREADS * CPT + 2) * sizeof(float));
+            cudaError_t e = cudaFuncSetAttribute(linear_scan_kernel<SCAN_WHOLE, CPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(linear_scan_kernel<SCAN_SEGMENTS, CPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(linear_scan_kernel<SCAN_FINISH, CPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+            if (e != cudaSuccess) return (int)e;
+            configured.mark();
+        }
+    }
+    const dim3 grid((p.V + cpb - 1) / cpb, p.H, rows * (cut ? p.nseg : 1));
+    if (!cut) return acorn_launch(linear_scan_kernel<SCAN_WHOLE, CPT>, grid, dim3(SCAN_THREADS), smem, stream, p);
+    const int rc = acorn_launch(linear_scan_kernel<SCAN_SEGMENTS, CPT>, grid, dim3(SCAN_THREADS), smem, stream, p);
+    if (rc != 0) return rc;
+    return acorn_launch(linear_scan_kernel<SCAN_FINISH, CPT>, grid, dim3(SCAN_THREADS), smem, stream, p);
+}
+
+// How many columns a thread of the scan holds for these sizes: a key read from shared memory serves all of
+// them, so more is less traffic, as long as the blocks still cover the columns without much waste.
+extern "C" int acorn_linear_scan_columns(int N, int V) {
+    int LN = 1;
+    while (LN * SCAN_STRIP < N) LN *= 2;
+    const int cpl = SCAN_THREADS / LN;
+    int most = 4;
+    if (const char* e = std::getenv("ACORN_SCAN_COLUMNS")) most = e[0] == '1' ? 1 : (e[0] == '2' ? 2 : 4);   // for experiments
+    return (most >= 4 && V >= 4 * cpl) ? 4 : ((most >= 2 && V >= 2 * cpl) ? 2 : 1);
 }
 
 // seg_tokens = 0: every row in one piece (seg_state, seg_decay unused).  Otherwise rows are cut into segments of
@@ -291,26 +351,13 @@ extern "C" int acorn_linear_scan(const float* b, int64_t ldb, const float* c, in
     if ((int64_t)rows * (cut ? nseg : 1) > 65535) return ACORN_ERR_UNSUPPORTED;
     int LN = 1;
     while (LN * SCAN_STRIP < N) LN *= 2;
-    const int cpb = SCAN_THREADS / LN;
     ScanParams p = {b, ldb, c, ldc, x, ldx, decay, lda, w, ldw, skip, state, slot_stride, state_off, y, row_start, row_slot,
                     H, G, N, V, LN, seg_state, seg_decay, seg_tokens, cut ? nseg : 1};
-    const size_t smem = (size_t)2 * SCAN_TOKENS * (2 * SCAN_STRIP * LN + cpb + 2) * sizeof(float);
-    if (smem > 48 * 1024) {
-        static AcornPerDevice configured;
-        if (!configured.seen()) {
-            const int most = (int)((size_t)2 * SCAN_TOKENS * (2 * 32 * SCAN_STRIP + 4 + 2) * sizeof(float));
-            cudaError_t e = cudaFuncSetAttribute(linear_scan_kernel<SCAN_WHOLE>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
-            if (e == cudaSuccess) e = cudaFuncSetAttribute(linear_scan_kernel<SCAN_SEGMENTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
-            if (e == cudaSuccess) e = cudaFuncSetAttribute(linear_scan_kernel<SCAN_FINISH>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
-            if (e != cudaSuccess) return (int)e;
-            configured.mark();
-        }
+    switch (acorn_linear_scan_columns(N, V)) {
+        case 4: return launch_scan<4>(p, rows, cut, stream);
+        case 2: return launch_scan<2>(p, rows, cut, stream);
+        default: return launch_scan<1>(p, rows, cut, stream);
     }
-    const dim3 grid((V + cpb - 1) / cpb, H, rows * (cut ? nseg : 1));
-    if (!cut) return acorn_launch(linear_scan_kernel<SCAN_WHOLE>, grid, dim3(SCAN_THREADS), smem, stream, p);
-    const int rc = acorn_launch(linear_scan_kernel<SCAN_SEGMENTS>, grid, dim3(SCAN_THREADS), smem, stream, p);
-    if (rc != 0) return rc;
-    return acorn_launch(linear_scan_kernel<SCAN_FINISH>, grid, dim3(SCAN_THREADS), smem, stream, p);
 }
 
 // y32 [T, W] in `groups` equal parts.  mode 0: u = y silu(z), out = u / rms_part(u) * weight;
