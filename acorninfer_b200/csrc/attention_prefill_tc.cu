@@ -47,6 +47,7 @@ struct AttnTcParams {
     const int* row_pos;
     const int* tiles;        // [n_tiles, 2]: row, first token of the tile within the row
     int table_stride, nq, nkv, logP, window;
+    int chunk;               // > 0: a query sees the keys of its own block of `chunk` positions only
     int n_tiles, pairs;      // pairs = ceil((nq / nkv) / 2): CTAs per (tile, kv head)
     float scale_log2;
 };
@@ -60,12 +61,13 @@ struct AttnTcParams {
 #define ATC_NUM_BARS (1 + 2 * ATC_SLOTS + 2 + 2 + 2)
 #define ATC_TMEM_COLS 512
 
-// -inf where the query at qpos may not see the key (causal, window, rows beyond the tile's queries)
-__device__ __forceinline__ void atc_mask(float (&s)[64], int key0, int qpos, bool row_ok, int window) {
+// -inf where the query at qpos may not see the key (causal, the first key its window or its block of positions
+// lets it see, rows beyond the tile's queries)
+__device__ __forceinline__ void atc_mask(float (&s)[64], int key0, int qpos, bool row_ok, int first_seen) {
 #pragma unroll
     for (int c = 0; c < 64; ++c) {
         const int key = key0 + c;
-        const bool okk = key <= qpos && row_ok && (window <= 0 || key > qpos - window);
+        const bool okk = key <= qpos && row_ok && key >= first_seen;
         s[c] = okk ? s[c] : -INFINITY;
     }
 }
@@ -150,6 +152,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
     const int pos0 = p.row_pos[r] + q0;
     const int hi = pos0 + n_q;                                           // keys < hi are read by the tile
     int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    if (p.chunk > 0) lo = max(lo, pos0 - pos0 % p.chunk);                // the first query's block of positions starts here
     lo &= ~(ATC_BN - 1);                                                 // blocks start at multiples of 128 keys
     const int nb = (hi - lo + ATC_BN - 1) / ATC_BN;
 
@@ -270,6 +273,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
         const int row = (warp & 3) * 32 + lane;                          // query row = TMEM lane
         const int head = head0 + u;
         const int qpos = pos0 + row;
+        const int first_seen = max(p.window > 0 ? qpos - p.window + 1 : 0, p.chunk > 0 ? qpos - qpos % p.chunk : 0);
         const bool row_ok = row < n_q;
         const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
         const uint32_t my_s = tmem_s + lane_addr + u * 128, my_o = tmem_o + lane_addr + u * 128;
@@ -284,7 +288,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
             tc_fence_after();
             const int key0 = lo + j * ATC_BN;
             // a block every query of the tile sees whole needs no mask
-            const bool masked = key0 + ATC_BN - 1 > pos0 || p.window > 0 || n_q < ATC_BM;
+            const bool masked = key0 + ATC_BN - 1 > pos0 || p.window > 0 || p.chunk > 0 || n_q < ATC_BM;
             // One pass in the common case: exponentiate against the reference maximum the row
             // already has while the block's own maximum is taken; only a row whose maximum
             // outgrew the reference by more than 2^8 (always so in its first block) moves the
@@ -293,11 +297,11 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
             uint32_t w_lo[32], w_hi[32];
             float neg_ref = m_ref == -INFINITY ? 0.f : -m_ref;
             tmem_ld64(my_s, s);
-            if (masked) atc_mask(s, key0, qpos, row_ok, p.window);
+            if (masked) atc_mask(s, key0, qpos, row_ok, first_seen);
             float mx = atc_max(s);
             float psum = atc_exp_pack(s, p.scale_log2, neg_ref, w_lo);
             tmem_ld64(my_s + 64, s);
-            if (masked) atc_mask(s, key0 + 64, qpos, row_ok, p.window);
+            if (masked) atc_mask(s, key0 + 64, qpos, row_ok, first_seen);
             mx = fmaxf(mx, atc_max(s)) * p.scale_log2;                   // the scale is positive
             float corr = 1.f;
             const bool grew = mx > m_ref + ATC_RESCALE_LOG2;
@@ -310,7 +314,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
                 }
                 psum = atc_exp_pack(s, p.scale_log2, neg_ref, w_hi);
                 tmem_ld64(my_s, s);
-                if (masked) atc_mask(s, key0, qpos, row_ok, p.window);
+                if (masked) atc_mask(s, key0, qpos, row_ok, first_seen);
                 psum += atc_exp_pack(s, p.scale_log2, neg_ref, w_lo);
             } else {
                 psum += atc_exp_pack(s, p.scale_log2, neg_ref, w_hi);
@@ -379,14 +383,14 @@ extern "C" int acorn_attention_prefill_tc(const void* q, int64_t q_stride, int t
                                           const void* v_pages, int64_t num_pages, const int* block_table,
                                           const int* page_base, int table_stride, const int* row_start,
                                           const int* row_pos, const int* tiles, int n_tiles, int nq, int nkv, int d,
-                                          int P, float scale, int window, cudaStream_t stream) {
+                                          int P, float scale, int window, int chunk, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (!acorn_attention_prefill_tc_supported(nq, nkv, d, P) || q_stride % 8 != 0 || ((uintptr_t)q & 15))
         return ACORN_ERR_UNSUPPORTED;
     AttnTcParams p;
     p.out = (bf16*)out; p.block_table = block_table; p.page_base = page_base; p.row_start = row_start;
     p.row_pos = row_pos; p.tiles = tiles; p.table_stride = table_stride; p.nq = nq; p.nkv = nkv;
-    p.logP = acorn_log2_exact_tc(P); p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
+    p.logP = acorn_log2_exact_tc(P); p.window = window; p.chunk = chunk; p.scale_log2 = scale * 1.4426950408889634f;
     p.n_tiles = n_tiles; p.pairs = (nq / nkv + 1) / 2;
     const int64_t ctas = (int64_t)n_tiles * nkv * p.pairs;
     if (ctas > 0x7fffffff) return ACORN_ERR_UNSUPPORTED;

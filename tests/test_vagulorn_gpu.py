@@ -286,7 +286,13 @@ def _attention_case(befores, qlens, P, d, dv, nq, nkv, rule, size, keep, spikes,
         i32 = dict(dtype=torch.int32, device=DEV)
         starts = np.cumsum([0] + qlens)
         out = torch.zeros((lay["num_tokens"], nq * d), dtype=dtype, device=DEV)
-        tiles = torch.tensor([(r, q0) for r, n in enumerate(qlens) if n > 1 for q0 in range(0, n, 64)], **i32).view(-1, 2)
+        big = 32 if kernel.startswith("tc") else 10 ** 9          # rows from 32 tokens on go to the tcgen05 kernel
+        tiles = torch.tensor([(r, q0) for r, n in enumerate(qlens) if n >= big for q0 in range(0, n, 128)], **i32).view(-1, 2)
+        if tiles.shape[0]:
+            assert keep == 0
+            o.attention_prefill_tc(q_new, nq * d, *common, torch.tensor(starts, **i32), torch.tensor(befores, **i32), tiles,
+                                   lay["num_tokens"], nq, nkv, d, scale, window, out=out, chunk=chunk)
+        tiles = torch.tensor([(r, q0) for r, n in enumerate(qlens) if 1 < n < big for q0 in range(0, n, 64)], **i32).view(-1, 2)
         if tiles.shape[0]:
             o.attention_prefill(q_new, nq * d, *common, torch.tensor(starts, **i32), torch.tensor(befores, **i32), tiles,
                                 lay["num_tokens"], nq, nkv, d, scale, window, out=out, chunk=chunk, keep_first=keep)
@@ -331,7 +337,7 @@ def test_attention_window_with_kept_first_keys(dtype, tol, kernel, d, dv, nq, nk
         assert (got - want).abs().max() < tol, (W2, keep2)
 
 
-@pytest.mark.parametrize("dtype,tol,kernel,d,dv,nq,nkv", KERNELS)
+@pytest.mark.parametrize("dtype,tol,kernel,d,dv,nq,nkv", KERNELS + [(torch.bfloat16, 2e-2, "tc2", 128, 128, 8, 2)])
 def test_attention_in_blocks_of_positions(dtype, tol, kernel, d, dv, nq, nkv):
     """Blocks are counted from position 0 of the request, wherever a portion starts: a spiked key is seen by the
     queries of its own block after it and by no other; far keys are never seen; no mask at all finds key 3 of 700."""
