@@ -37,6 +37,7 @@ __device__ int g_gemm_tc_error = 0;
 #define TC_MODE_SWIGLU 2      // tiles of 64 gate + 64 up columns: out = silu(gate) * up
 #define TC_MODE_QKV_ROPE 3    // tiles are heads of 128: q/k RMSNorm + rotation; k and v to their cache pages
 #define TC_MODE_SWIGLU_PAIRS 4   // columns 2i and 2i + 1 are the gate and the up value of output i
+#define TC_MODE_GEGLU 5       // as TC_MODE_SWIGLU with the tanh form of gelu: out = gelu(gate) * up
 // reduction scratch of the epilogues (floats): four partial sums a row, or a head and its partial sums
 #define TC_RED_FLOATS(MB) (4 * (MB) > 256 ? 4 * (MB) : 256)
 
@@ -312,15 +313,17 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
                 else reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(val);
             }
         }
-    } else if (p.mode == TC_MODE_SWIGLU) {
+    } else if (p.mode == TC_MODE_SWIGLU || p.mode == TC_MODE_GEGLU) {
         // the tile holds 64 gate columns, then the 64 up columns of the same outputs
         for (int i = 0, m = rank; m < m_valid; ++i, m += csize) {
             if (col < 64) {
                 const float g = tile_sum(i, col) * inv_s[m], u = tile_sum(i, col + 64) * inv_s[m];
                 const int oc = blockIdx.x * 64 + col;
+                // gelu's tanh form is g sigmoid(2 sqrt(2/pi) (g + 0.044715 g^3))
+                const float z = p.mode == TC_MODE_GEGLU ? 1.5957691216057308f * (g + 0.044715f * g * g * g) : g;
                 if (oc < p.N / 2)
                     reinterpret_cast<bf16*>(p.out)[(int64_t)(m0 + m) * p.ldo + oc] =
-                        __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
+                        __float2bfloat16_rn(g / (1.f + expf(-z)) * u);
             }
         }
     } else if (p.mode == TC_MODE_SWIGLU_PAIRS) {
@@ -486,8 +489,8 @@ extern "C" int acorn_gemm_tc_ex(const void* x, int64_t ldx, const void* w, int64
                                 int N, int K, int out_f32, int splits, int per_sm, int mode, const float* ss_in, int ss_parts,
                                 int norm_width, float eps, float* resid, int64_t ldr, const float* norm_w,
                                 float* ss_out, cudaStream_t stream) {
-    if (mode != TC_MODE_PLAIN && mode != TC_MODE_ADD_NORM && mode != TC_MODE_SWIGLU) return ACORN_ERR_UNSUPPORTED;
-    if (mode == TC_MODE_SWIGLU && N % 128 != 0) return ACORN_ERR_UNSUPPORTED;
+    if (mode != TC_MODE_PLAIN && mode != TC_MODE_ADD_NORM && mode != TC_MODE_SWIGLU && mode != TC_MODE_GEGLU) return ACORN_ERR_UNSUPPORTED;
+    if ((mode == TC_MODE_SWIGLU || mode == TC_MODE_GEGLU) && N % 128 != 0) return ACORN_ERR_UNSUPPORTED;
     if (mode == TC_MODE_ADD_NORM && (resid == nullptr || norm_w == nullptr || ss_out == nullptr)) return ACORN_ERR_UNSUPPORTED;
     TcParams p = {};
     p.out = out; p.ldo = ldo; p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32;

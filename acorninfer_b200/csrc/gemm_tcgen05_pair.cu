@@ -46,6 +46,7 @@
 #define G2_MODE_ADD_NORM 1    // residual += product; out = bf16(residual * norm_w); ss_out = the tile's share of sum(residual^2)
 #define G2_MODE_SWIGLU 2      // W in blocks of 64 gate rows + 64 up rows: out = silu(gate) * up, N / 2 columns
 #define G2_MODE_QKV_ROPE 3    // W rows are heads of 128: q/k RMSNorm + rotation; k and v to their cache pages
+#define G2_MODE_GEGLU 5       // as G2_MODE_SWIGLU with the tanh form of gelu: out = gelu(gate) * up
 
 __device__ int g_gemm_pair_error = 0;
 
@@ -283,7 +284,7 @@ __global__ void __launch_bounds__(G2_THREADS, 1) gemm_tcgen05_pair_kernel(const 
                         else store_chunk_bf16(reinterpret_cast<bf16*>(p.out) + (int64_t)m * p.ldo + n0 + c, v, nv);
                     }
                 }
-            } else if (p.mode == G2_MODE_SWIGLU) {
+            } else if (p.mode == G2_MODE_SWIGLU || p.mode == G2_MODE_GEGLU) {
                 // W rows n0 .. n0 + 255 are two blocks of 64 gate rows and 64 up rows: 128 outputs
                 {
                     const int b = half;
@@ -299,7 +300,9 @@ __global__ void __launch_bounds__(G2_THREADS, 1) gemm_tcgen05_pair_kernel(const 
 #pragma unroll
                             for (int j = 0; j < 32; ++j) {
                                 const float gv = gt[j] * inv, uv = up[j] * inv;
-                                gt[j] = gv / (1.f + expf(-gv)) * uv;
+                                // gelu's tanh form is g sigmoid(2 sqrt(2/pi) (g + 0.044715 g^3))
+                                const float z = p.mode == G2_MODE_GEGLU ? 1.5957691216057308f * (gv + 0.044715f * gv * gv * gv) : gv;
+                                gt[j] = gv / (1.f + expf(-z)) * uv;
                             }
                             store_chunk_bf16(reinterpret_cast<bf16*>(p.out) + (int64_t)m * p.ldo + oc, gt, nv);
                         }
@@ -494,9 +497,9 @@ extern "C" int acorn_gemm_tc_pair(const void* x, int64_t ldx, const void* w, int
                                   int N, int K, int out_f32, int pairs, int mode, const float* ss_in, int ss_parts,
                                   int norm_width, float eps, float* resid, int64_t ldr, const float* norm_w,
                                   float* ss_out, cudaStream_t stream) {
-    if (mode != G2_MODE_PLAIN && mode != G2_MODE_ADD_NORM && mode != G2_MODE_SWIGLU) return ACORN_ERR_UNSUPPORTED;
+    if (mode != G2_MODE_PLAIN && mode != G2_MODE_ADD_NORM && mode != G2_MODE_SWIGLU && mode != G2_MODE_GEGLU) return ACORN_ERR_UNSUPPORTED;
     if (mode != G2_MODE_PLAIN && out_f32) return ACORN_ERR_UNSUPPORTED;
-    if (mode == G2_MODE_SWIGLU && N % 128 != 0) return ACORN_ERR_UNSUPPORTED;
+    if ((mode == G2_MODE_SWIGLU || mode == G2_MODE_GEGLU) && N % 128 != 0) return ACORN_ERR_UNSUPPORTED;
     if (mode == G2_MODE_ADD_NORM && (resid == nullptr || norm_w == nullptr || ss_out == nullptr)) return ACORN_ERR_UNSUPPORTED;
     G2Params p = {};
     p.out = out; p.ldo = ldo; p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32;

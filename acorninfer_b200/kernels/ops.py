@@ -850,12 +850,14 @@ def rope_kv_fusable(num_rows: int, dtype: torch.dtype, head_dim: int, rotary_dim
 
 def gemm_tc(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, splits: int | None = None,
             out: torch.Tensor | None = None, epilogue: AddNormEpilogue | None = None, swiglu: bool = False,
+            activation: str = "silu",
             per_sm: int = 2):
     """x [M, K] @ w [N, K]^T on tcgen05 tensor cores (bfloat16 in, float32 accumulate).
 
     ``x`` may be ``NormedRows`` (at most 64 rows): the rows' RMS factors are applied to the product.
     ``epilogue``: see ``AddNormEpilogue`` (returns ``NormedRows``).  ``swiglu``: ``w`` holds blocks
-    of 64 gate rows and 64 up rows; returns ``silu(gate) * up`` [M, N / 2]."""
+    of 64 gate rows and 64 up rows; returns ``act(gate) * up`` [M, N / 2], ``act`` by ``activation`` (silu or the
+    tanh form of gelu)."""
     rows = x if isinstance(x, NormedRows) else None
     xt = rows.x if rows is not None else x
     if not gemm_tc_supported(xt, w):
@@ -883,7 +885,7 @@ def gemm_tc(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, splits:
     elif swiglu:
         if N % 128 or out_dtype != torch.bfloat16:
             raise KernelError("gemm_tc: SwiGLU epilogue needs N a multiple of 128 and bfloat16 output")
-        mode, out_cols = 2, N // 2
+        mode, out_cols = (2, 5)[GLU_ACTIVATIONS[activation]], N // 2
     if out is None:
         out = torch.empty((M, out_cols), dtype=out_dtype, device=xt.device)
     _check(out, "out", out_dtype, 2)
@@ -899,7 +901,8 @@ def gemm_tc(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, splits:
 
 
 def gemm_tc_pair(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, out: torch.Tensor | None = None,
-                 epilogue: AddNormEpilogue | None = None, swiglu: bool = False, pairs: int | None = None):
+                 epilogue: AddNormEpilogue | None = None, swiglu: bool = False, pairs: int | None = None,
+                 activation: str = "silu"):
     """x [M, K] @ w [N, K]^T in bfloat16 on pairs of CTAs (tcgen05 ``cta_group::2``), for many rows:
     tiles of 256 rows of ``x`` by 256 rows of ``w``, one pair of SMs to a tile at a time.  ``x`` as
     ``NormedRows``, ``epilogue`` and ``swiglu`` as in ``gemm_tc``."""
@@ -926,7 +929,7 @@ def gemm_tc_pair(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, ou
     elif swiglu:
         if N % 128 or out_dtype != torch.bfloat16:
             raise KernelError("gemm_tc_pair: SwiGLU epilogue needs N a multiple of 128 and bfloat16 output")
-        mode, out_cols = 2, N // 2
+        mode, out_cols = (2, 5)[GLU_ACTIVATIONS[activation]], N // 2
     if out is None:
         out = torch.empty((M, out_cols), dtype=out_dtype, device=xt.device)
     _check(out, "out", out_dtype, 2)
@@ -969,7 +972,7 @@ def fused_rows_ok(num_rows: int, dtype: torch.dtype, widths=None, num_sms: int =
 
 
 def linear(x, w: torch.Tensor, out_dtype: torch.dtype | None = None, epilogue: AddNormEpilogue | None = None,
-           swiglu: bool = False, residual32: torch.Tensor | None = None):
+           swiglu: bool = False, residual32: torch.Tensor | None = None, activation: str = "silu"):
     """x [T, K] times w [N, K] transposed.
 
     float32 operands: the CUDA-core kernel (no reduced-precision matrix mode).
@@ -978,7 +981,8 @@ def linear(x, w: torch.Tensor, out_dtype: torch.dtype | None = None, epilogue: A
     ``out_dtype=float32`` keeps the accumulator's precision (used for logits).
     A weight stored in float32 under a bfloat16 engine is multiplied in float32.
     ``x`` as ``NormedRows``, ``epilogue`` and ``swiglu`` exist on the tcgen05 kernels only: the one-CTA
-    kernel up to GEMM_TC_MAX_ROWS rows, the paired kernel above (callers ask ``fused_rows_ok`` whether
+    kernel up to GEMM_TC_MAX_ROWS rows, the paired kernel above (``activation``: the gate's function under
+    ``swiglu``; callers ask ``fused_rows_ok`` whether
     that pays for their sizes); asking for them with other operands is an error, not a silent detour.
     ``residual32`` ([T, N] float32) is an offer: where the product goes to the library it is
     added to ``residual32`` in place, in float32 (the library's C operand: the product is not
@@ -992,8 +996,8 @@ def linear(x, w: torch.Tensor, out_dtype: torch.dtype | None = None, epilogue: A
             raise KernelError(f"linear: fused epilogues need a tcgen05 path (bf16, K a multiple of 8); got "
                               f"{tuple(xt.shape)} {xt.dtype} x {tuple(w.shape)} {w.dtype}")
         if xt.shape[0] > GEMM_TC_MAX_ROWS:
-            return gemm_tc_pair(x, w, out_dtype, epilogue=epilogue, swiglu=swiglu)
-        return gemm_tc(x, w, out_dtype, epilogue=epilogue, swiglu=swiglu)
+            return gemm_tc_pair(x, w, out_dtype, epilogue=epilogue, swiglu=swiglu, activation=activation)
+        return gemm_tc(x, w, out_dtype, epilogue=epilogue, swiglu=swiglu, activation=activation)
     if w.dtype == torch.float32:
         y = gemm_f32(cast(x, torch.float32) if x.dtype != torch.float32 else x, w)
         return y if out_dtype == torch.float32 else cast(y, out_dtype)

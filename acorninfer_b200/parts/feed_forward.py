@@ -52,8 +52,7 @@ class SwiGLU(FeedForward):
 
     def fusable(self, num_rows):
         widths = (2 * self.intermediate_size, self.hidden_size)                 # of the gate/up product and of the down product
-        return (self.activation == "silu"        # the products' epilogue applies silu only
-                and ops.fused_rows_ok(num_rows, self.ctx.dtype, widths, ops.device_sms(self.ctx.device))
+        return (ops.fused_rows_ok(num_rows, self.ctx.dtype, widths, ops.device_sms(self.ctx.device))
                 and self.w_gate_up.dtype == torch.bfloat16
                 and self.w_down.dtype == torch.bfloat16 and self.hidden_size % 8 == 0
                 and self.intermediate_size % 8 == 0)
@@ -72,8 +71,8 @@ class SwiGLU(FeedForward):
 
     def forward(self, x, inputs, epilogue=None, residual32=None):
         rows = x.x.shape[0] if isinstance(x, ops.NormedRows) else x.shape[0]
-        if self.block == 64 and self.activation == "silu" and (self.fusable(rows) or self._gate_up_fuses(rows)):
-            h = ops.linear(x, self.w_gate_up, out_dtype=self.ctx.dtype, swiglu=True)
+        if self.block == 64 and (self.fusable(rows) or self._gate_up_fuses(rows)):
+            h = ops.linear(x, self.w_gate_up, out_dtype=self.ctx.dtype, swiglu=True, activation=self.activation)
         else:
             gu = ops.linear(x, self.w_gate_up, out_dtype=self.ctx.dtype)
             h = ops.swiglu(gu, block=self.block, activation=self.activation)

@@ -457,3 +457,20 @@ def test_gated_norm_layernorm_glu_and_head_gate(dtype, tol):
     o.head_gate(xh.to(DEV), gate.to(DEV), heads, 0.8, out=wide[:, 16:])
     want = xh.double().view(T, heads, d) * (0.8 * torch.sigmoid(gate[:, :heads].double()))[:, :, None]
     assert (wide[:, 16:].cpu().double().view(T, heads, d) - want).abs().max() < tol * 4
+
+
+@pytest.mark.parametrize("M", [5, 32, 700])
+def test_gelu_gate_as_the_epilogue_of_the_tensor_core_products(M):
+    """gate and up rows in blocks of 64: the product's own epilogue applies the tanh form of gelu to the gate
+    (the one-CTA kernel for few rows, the paired kernel for many)."""
+    o = ops()
+    g = torch.Generator().manual_seed(M)
+    K, I = 96, 192
+    x = (torch.randn(M, K, generator=g) * 0.5).to(torch.bfloat16)
+    wg, wu = (torch.randn(I, K, generator=g) * 0.2).to(torch.bfloat16), (torch.randn(I, K, generator=g) * 0.2).to(torch.bfloat16)
+    w = torch.stack([wg.view(I // 64, 64, K), wu.view(I // 64, 64, K)], dim=1).reshape(2 * I, K).contiguous()
+    got = o.linear(x.to(DEV), w.to(DEV), out_dtype=torch.bfloat16, swiglu=True, activation="gelu_tanh").float().cpu()
+    want = plain.gelu_tanh(x.double() @ wg.double().T) * (x.double() @ wu.double().T)
+    assert got.shape == (M, I) and (got.double() - want).abs().max() < 3e-2 * float(want.abs().max())
+    silu = o.linear(x.to(DEV), w.to(DEV), out_dtype=torch.bfloat16, swiglu=True).float().cpu()
+    assert (silu.double() - plain.silu(x.double() @ wg.double().T) * (x.double() @ wu.double().T)).abs().max() < 3e-2 * float(want.abs().max())
