@@ -421,10 +421,41 @@ __global__ void head_gate_kernel(const T* x, const T* __restrict__ g, int64_t ld
     }
 }
 
+// The same, 16 bytes of a head to a thread (head sizes and row strides that are multiples of 16 bytes).
+template <typename T>
+__global__ void head_gate_vec_kernel(const T* x, const T* __restrict__ g, int64_t ldg, T* out, int64_t ldo, int heads,
+                                     int d, int64_t total_vecs, float scale) {
+    constexpr int VEC = 16 / (int)sizeof(T);
+    pdl_wait();
+    pdl_trigger();
+    const int row_vecs = heads * d / VEC, head_vecs = d / VEC;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_vecs; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = i / row_vecs;
+        const int in_row = (int)(i - t * row_vecs);
+        const float f = g ? scale / (1.f + expf(-to_float(g[t * ldg + in_row / head_vecs]))) : scale;
+        const uint4 raw = *reinterpret_cast<const uint4*>(x + t * (int64_t)heads * d + (int64_t)in_row * VEC);
+        const T* v = reinterpret_cast<const T*>(&raw);
+        uint4 res;
+        T* o = reinterpret_cast<T*>(&res);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) o[k] = from_float<T>(to_float(v[k]) * f);
+        *reinterpret_cast<uint4*>(out + t * ldo + (int64_t)in_row * VEC) = res;
+    }
+}
+
 extern "C" int acorn_head_gate(const void* x, const void* g, int64_t ldg, void* out, int64_t ldo, int tokens, int heads,
                                int d, float scale, int dtype, cudaStream_t stream) {
     const int64_t total = (int64_t)tokens * heads * d;
     if (total <= 0) return 0;
+    const int vec = dtype == ACORN_DTYPE_F32 ? 4 : 8;
+    if (d % vec == 0 && ldo % vec == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+        const int64_t vecs = total / vec;
+        int64_t blocks = (vecs + 255) / 256;
+        if (blocks > 148 * 16) blocks = 148 * 16;
+        ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(head_gate_vec_kernel<T>, dim3((int)blocks), dim3(256), 0, stream,
+                                                           (const T*)x, (const T*)g, ldg, (T*)out, ldo, heads, d, vecs,
+                                                           scale));
+    }
     int64_t blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(head_gate_kernel<T>, dim3((int)blocks), dim3(256), 0, stream,
