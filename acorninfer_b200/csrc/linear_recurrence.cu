@@ -123,8 +123,31 @@ struct ScanParams {
 #define SCAN_SEGMENTS 1     // every segment but a row's last: its end state and the product of its decays
 #define SCAN_FINISH 2       // every segment from the state it really starts with: y, and the row's last state
 
+// Two float32 numbers in a 64-bit register and the packed instructions on them (each half as the scalar
+// instruction rounds it): half the issue slots for the scan's multiply-adds.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 __device__ __forceinline__ void scan_cp4(float* dst, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src));
+}
+__device__ __forceinline__ void scan_cp16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src));
 }
 
 // A recurrence runs over a row's tokens one after the other; what runs side by side is heads, columns
@@ -164,24 +187,27 @@ __global__ void __launch_bounds__(SCAN_THREADS, CPT == 4 ? 3 : 4) linear_scan_ke
     float* seg_states = MODE == SCAN_WHOLE ? nullptr : p.seg_state + (int64_t)r * (p.nseg + 1) * HVN;
     // column j of the thread is v0 + col + j * cpl; its state entries start at strip0 + j * strip_step within [H, V, N]
     const int64_t strip0 = ((int64_t)h * p.V + v0 + col) * p.N, strip_step = (int64_t)cpl * p.N;
-    float s[CPT][SCAN_STRIP];
+    f32x2 s[CPT][SCAN_STRIP / 2];                       // entries 2k and 2k + 1 of the thread's strip in s[j][k]
 #define SCAN_LIVE(j) (v0 + col + (j) * cpl < p.V)
 #define SCAN_AT(j) (strip0 + (j) * strip_step)
 #pragma unroll
     for (int j = 0; j < CPT; ++j) {
+        float e[SCAN_STRIP];
 #pragma unroll
         for (int i = 0; i < SCAN_STRIP; ++i) {
             const int n = (i >> 2) * 4 * p.LN + 4 * l + (i & 3);
             const bool ok = SCAN_LIVE(j) && n < p.N;
             if (MODE == SCAN_WHOLE) {
-                s[j][i] = ok ? slot[SCAN_AT(j) + n] : 0.f;
+                e[i] = ok ? slot[SCAN_AT(j) + n] : 0.f;
             } else if (MODE == SCAN_SEGMENTS) {
-                s[j][i] = (ok && sg == 0) ? slot[SCAN_AT(j) + n] : 0.f;
-                if (ok && sg == 0) seg_states[SCAN_AT(j) + n] = s[j][i];          // the row's state before the step
+                e[i] = (ok && sg == 0) ? slot[SCAN_AT(j) + n] : 0.f;
+                if (ok && sg == 0) seg_states[SCAN_AT(j) + n] = e[i];             // the row's state before the step
             } else {
-                s[j][i] = ok ? seg_states[(sg == 0 ? 0 : HVN) + SCAN_AT(j) + n] : 0.f;
+                e[i] = ok ? seg_states[(sg == 0 ? 0 : HVN) + SCAN_AT(j) + n] : 0.f;
             }
         }
+#pragma unroll
+        for (int k = 0; k < SCAN_STRIP / 2; ++k) s[j][k] = pack2(e[2 * k], e[2 * k + 1]);
     }
     if (MODE == SCAN_SEGMENTS && sg == nseg_r - 1) return;      // a row of one segment: only its state was copied
     if (MODE == SCAN_FINISH) {
@@ -190,14 +216,22 @@ __global__ void __launch_bounds__(SCAN_THREADS, CPT == 4 ? 3 : 4) linear_scan_ke
 #pragma unroll
             for (int j = 0; j < CPT; ++j)
 #pragma unroll
-                for (int i = 0; i < SCAN_STRIP; ++i) {
-                    const int n = (i >> 2) * 4 * p.LN + 4 * l + (i & 3);
-                    if (SCAN_LIVE(j) && n < p.N) s[j][i] = fmaf(pk, s[j][i], seg_states[(int64_t)(k + 1) * HVN + SCAN_AT(j) + n]);
+                for (int i = 0; i < SCAN_STRIP; i += 2) {
+                    float e[2];
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) {
+                        const int n = ((i + q) >> 2) * 4 * p.LN + 4 * l + ((i + q) & 3);
+                        e[q] = (SCAN_LIVE(j) && n < p.N) ? seg_states[(int64_t)(k + 1) * HVN + SCAN_AT(j) + n] : 0.f;
+                    }
+                    s[j][i / 2] = fma2(pack2(pk, pk), s[j][i / 2], pack2(e[0], e[1]));
                 }
         }
     }
     const float skip = p.skip ? p.skip[h] : 0.f;
     float prod = 1.f;
+    // keys whose rows start on 16-byte boundaries are copied 16 bytes at a time
+    const bool keys16 = (p.N & 3) == 0 && (p.ldb & 3) == 0 && (p.ldc & 3) == 0 &&
+                        ((reinterpret_cast<uintptr_t>(p.b) | reinterpret_cast<uintptr_t>(p.c)) & 15) == 0;
     auto stage_in = [&](int t0, int stage) {
         float* sB = sm + stage * stage_floats;                  // [SCAN_TOKENS][NS]
         float* sC = sB + SCAN_TOKENS * NS;
@@ -206,11 +240,22 @@ __global__ void __launch_bounds__(SCAN_THREADS, CPT == 4 ? 3 : 4) linear_scan_ke
         float* sW = sA + SCAN_TOKENS;
         const int nt = min(SCAN_TOKENS, L - t0);
         if (nt > 0) {
+            if (keys16) {                                       // 16 bytes a copy: a token's keys in N / 4 pieces
+                const int per = p.N >> 2;
+                for (int i = threadIdx.x; i < nt * per; i += SCAN_THREADS) {
+                    const int tt = i / per, n = (i - tt * per) << 2;
+                    const int64_t tok = first + t0 + tt;
+                    scan_cp16(sB + tt * NS + n, p.b + tok * p.ldb + (int64_t)g * p.N + n);
+                    if (MODE != SCAN_SEGMENTS) scan_cp16(sC + tt * NS + n, p.c + tok * p.ldc + (int64_t)g * p.N + n);
+                }
+            }
             for (int tt = 0; tt < nt; ++tt) {
                 const int64_t tok = first + t0 + tt;
-                for (int n = threadIdx.x; n < p.N; n += SCAN_THREADS) {
-                    scan_cp4(sB + tt * NS + n, p.b + tok * p.ldb + (int64_t)g * p.N + n);
-                    if (MODE != SCAN_SEGMENTS) scan_cp4(sC + tt * NS + n, p.c + tok * p.ldc + (int64_t)g * p.N + n);
+                if (!keys16) {
+                    for (int n = threadIdx.x; n < p.N; n += SCAN_THREADS) {
+                        scan_cp4(sB + tt * NS + n, p.b + tok * p.ldb + (int64_t)g * p.N + n);
+                        if (MODE != SCAN_SEGMENTS) scan_cp4(sC + tt * NS + n, p.c + tok * p.ldc + (int64_t)g * p.N + n);
+                    }
                 }
                 for (int cc = threadIdx.x; cc < cpb; cc += SCAN_THREADS) {
                     if (v0 + cc < p.V) scan_cp4(sX + tt * cpb + cc, p.x + tok * p.ldx + (int64_t)h * p.V + v0 + cc);
@@ -240,35 +285,40 @@ __global__ void __launch_bounds__(SCAN_THREADS, CPT == 4 ? 3 : 4) linear_scan_ke
         const int nt = min(SCAN_TOKENS, L - t0);
         for (int tt = 0; tt < nt; ++tt) {
             const float a = sA[tt], wt = sW[tt];
-            float xv[CPT], u[CPT], acc[CPT];
+            float xv[CPT];
+            f32x2 uu[CPT], acc2[CPT];
+            const f32x2 aa = pack2(a, a);
 #pragma unroll
             for (int j = 0; j < CPT; ++j) {
                 xv[j] = sX[tt * cpb + col + j * cpl];
-                u[j] = wt * xv[j];
-                acc[j] = 0.f;
+                uu[j] = pack2(wt * xv[j], wt * xv[j]);
+                acc2[j] = 0ull;
             }
-            const float4* bb = reinterpret_cast<const float4*>(sB + tt * NS) + l;
-            const float4* cc = reinterpret_cast<const float4*>(sC + tt * NS) + l;
+            const ulonglong2* bb = reinterpret_cast<const ulonglong2*>(sB + tt * NS) + l;
+            const ulonglong2* cc = reinterpret_cast<const ulonglong2*>(sC + tt * NS) + l;
             // entries beyond N hold zeros and stay zero (their keys are zeros); a key is read once for the
-            // thread's CPT columns
+            // thread's CPT columns; the arithmetic is on pairs of entries (packed float32x2)
 #pragma unroll
             for (int i4 = 0; i4 < SCAN_STRIP / 4; ++i4) {
-                const float4 b4 = bb[i4 * p.LN];
-                float4 c4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                const ulonglong2 b4 = bb[i4 * p.LN];
+                ulonglong2 c4 = make_ulonglong2(0ull, 0ull);
                 if (MODE != SCAN_SEGMENTS) c4 = cc[i4 * p.LN];
 #pragma unroll
                 for (int j = 0; j < CPT; ++j) {
-                    s[j][4 * i4] = fmaf(a, s[j][4 * i4], b4.x * u[j]);
-                    s[j][4 * i4 + 1] = fmaf(a, s[j][4 * i4 + 1], b4.y * u[j]);
-                    s[j][4 * i4 + 2] = fmaf(a, s[j][4 * i4 + 2], b4.z * u[j]);
-                    s[j][4 * i4 + 3] = fmaf(a, s[j][4 * i4 + 3], b4.w * u[j]);
+                    s[j][2 * i4] = fma2(aa, s[j][2 * i4], mul2(b4.x, uu[j]));
+                    s[j][2 * i4 + 1] = fma2(aa, s[j][2 * i4 + 1], mul2(b4.y, uu[j]));
                     if (MODE != SCAN_SEGMENTS) {
-                        acc[j] = fmaf(s[j][4 * i4], c4.x, acc[j]);
-                        acc[j] = fmaf(s[j][4 * i4 + 1], c4.y, acc[j]);
-                        acc[j] = fmaf(s[j][4 * i4 + 2], c4.z, acc[j]);
-                        acc[j] = fmaf(s[j][4 * i4 + 3], c4.w, acc[j]);
+                        acc2[j] = fma2(s[j][2 * i4], c4.x, acc2[j]);
+                        acc2[j] = fma2(s[j][2 * i4 + 1], c4.y, acc2[j]);
                     }
                 }
+            }
+            float acc[CPT];
+#pragma unroll
+            for (int j = 0; j < CPT; ++j) {
+                float lo, hi;
+                unpack2(acc2[j], lo, hi);
+                acc[j] = lo + hi;
             }
             if (MODE == SCAN_SEGMENTS) {
                 prod *= a;
@@ -292,9 +342,14 @@ __global__ void __launch_bounds__(SCAN_THREADS, CPT == 4 ? 3 : 4) linear_scan_ke
     for (int j = 0; j < CPT; ++j) {
         if (!SCAN_LIVE(j)) continue;
 #pragma unroll
-        for (int i = 0; i < SCAN_STRIP; ++i) {
-            const int n = (i >> 2) * 4 * p.LN + 4 * l + (i & 3);
-            if (n < p.N) dst[SCAN_AT(j) + n] = s[j][i];
+        for (int i = 0; i < SCAN_STRIP; i += 2) {
+            float e[2];
+            unpack2(s[j][i / 2], e[0], e[1]);
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                const int n = ((i + q) >> 2) * 4 * p.LN + 4 * l + ((i + q) & 3);
+                if (n < p.N) dst[SCAN_AT(j) + n] = e[q];
+            }
         }
     }
     if (MODE == SCAN_SEGMENTS && blockIdx.x == 0 && threadIdx.x == 0)
@@ -331,7 +386,9 @@ extern "C" int acorn_linear_scan_columns(int N, int V) {
     int LN = 1;
     while (LN * SCAN_STRIP < N) LN *= 2;
     const int cpl = SCAN_THREADS / LN;
-    int most = 4;
+    // two measured as fast as four with segments (2,048 tokens: 505 / 277 us against 492 / 313 us for the two mixers
+    // at width 2,048) and a third faster on a row in one piece (849 against 1,232 us)
+    int most = 2;
     if (const char* e = std::getenv("ACORN_SCAN_COLUMNS")) most = e[0] == '1' ? 1 : (e[0] == '2' ? 2 : 4);   // for experiments
     return (most >= 4 && V >= 4 * cpl) ? 4 : ((most >= 2 && V >= 2 * cpl) ? 2 : 1);
 }

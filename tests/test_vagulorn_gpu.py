@@ -318,7 +318,7 @@ def test_attention_window_with_kept_first_keys(dtype, tol, kernel, d, dv, nq, nk
     """A key that outweighs all others is seen up to the query window - 1 tokens after it and no longer, in a
     prompt's rows and in single decoded tokens, at page borders; the first ``keep`` keys are seen from
     anywhere and the next one is not."""
-    P, W, keep = 16, 64, 6
+    P, W, keep = 16, 64, 5
     # row 0: a whole prompt; row 1: a portion after 130 cached tokens; rows 2-5: single tokens whose window's
     # first key (2, 4) or the key just before it (3, 5) is the spiked one, at a page's border or not; rows 6, 7:
     # single tokens far away whose spiked key is the last kept one (6) or the first that is not kept (7)

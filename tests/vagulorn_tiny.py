@@ -57,7 +57,7 @@ VAGU_B = dict(page_size=4, seed=8, cfg=VagulornConfig(
 VAGU_C = dict(page_size=16, seed=9, cfg=VagulornConfig(
     vocab_size=320, hidden_size=128, norm_eps=1e-5, embedding_scale=8.0, layers=(
         L(StateSpaceConfig(heads=4, vdim=32, state=64, groups=2, conv=3, norm_groups=2), ff=192),
-        L(beside(att(heads=4, kv_heads=2, dim=64, vdim=64, scale=0.125, rot_dims=32, rot_base=5e5, mask_size=40,
+        L(beside(att(heads=4, kv_heads=2, dim=64, vdim=64, scale=0.125, rot_dims=32, rot_base=3e5, mask_size=40,
                      keep_first=5), heads=2, dim=32, vdim=48, decay=(0.7, 0.995), left_scale=0.8, right_scale=0.9), ff=192),
         L(att(heads=6, kv_heads=3, dim=32, vdim=32, scale=0.18, rot_dims=16, rot_base=1e4, mask_size=24), ff=128),
         L(att(heads=2, kv_heads=1, dim=48, vdim=80, scale=0.15, rot_dims=48, rot_base=1e4, mask_size=50), ff=None),
