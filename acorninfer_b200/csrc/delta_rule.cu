@@ -106,13 +106,14 @@ extern "C" int acorn_delta_prep(const void* main_, int64_t ld, const float* up, 
 template <typename T>
 __global__ void conv_state_update_kernel(const T* __restrict__ main_, int64_t ld, float* __restrict__ state,
                                          int64_t slot_stride, int64_t conv_off, const int* __restrict__ row_start,
-                                         const int* __restrict__ row_slot, int C, int taps) {
+                                         const int* __restrict__ row_slot, int C, int taps, int skip_single) {
     pdl_wait();
     pdl_trigger();
     const int r = blockIdx.y;
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= C) return;
     const int first = row_start[r], L = row_start[r + 1] - first;
+    if (skip_single && L == 1) return;                  // the kernel before this one has shifted the memory of such rows
     float* cs = state + (int64_t)row_slot[r] * slot_stride + conv_off;
     float keep[DELTA_MAX_TAPS];
 #pragma unroll
@@ -129,13 +130,13 @@ __global__ void conv_state_update_kernel(const T* __restrict__ main_, int64_t ld
 
 extern "C" int acorn_conv_state_update(const void* main_, int64_t ld, float* state, int64_t slot_stride, int64_t conv_off,
                                        const int* row_start, const int* row_slot, int rows, int C, int taps, int dtype,
-                                       cudaStream_t stream) {
+                                       int skip_single, cudaStream_t stream) {
     if (rows <= 0 || taps <= 1) return 0;
     if (taps > DELTA_MAX_TAPS || rows > 65535) return ACORN_ERR_UNSUPPORTED;
     dim3 grid((C + 127) / 128, rows);
     ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(conv_state_update_kernel<T>, grid, dim3(128), 0, stream,
                                                        (const T*)main_, ld, state, slot_stride, conv_off, row_start,
-                                                       row_slot, C, taps));
+                                                       row_slot, C, taps, skip_single));
     return ACORN_ERR_UNSUPPORTED;
 }
 

@@ -12,7 +12,8 @@
 //
 //   ssm_prep        per token: the short causal convolution over time of the x, B, C channels (inputs
 //                   before the step's first token come from the request's state) with bias, silu;
-//                   dt = softplus(. + dt_bias) and a = exp(-exp(A_log) dt); float32 outputs
+//                   dt = softplus(. + dt_bias) and a = exp(-exp(A_log) dt); float32 outputs; on request it
+//                   also shifts the convolution's memory of rows of one token
 //   silu_rows       out32 = silu(in) (the q, k, v of the linear attention)
 //   linear_scan     the recurrence over a row's tokens, state in registers
 //   gated_norm      per token: RMS norm in equal groups of the row with a weight, and a gate either
@@ -29,6 +30,7 @@
 #define SCAN_STRIP 16                   // state entries of a column a thread holds
 #define SCAN_TOKENS 8                   // tokens staged at a time
 #define SSM_MAX_TAPS 16
+#define SSM_PREP_CHANNELS 512
 
 __device__ __forceinline__ float lr_sigmoid(float z) { return 1.f / (1.f + expf(-z)); }
 __device__ __forceinline__ float lr_softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
@@ -36,18 +38,23 @@ __device__ __forceinline__ float lr_softplus(float z) { return z > 20.f ? z : lo
 // in [T, ld]: the convolution's C channels start at column c0, the H step-size pre-activations at column dt0.
 template <typename T>
 __global__ void ssm_prep_kernel(const T* __restrict__ in, int64_t ld, int c0, int dt0, const float* __restrict__ conv_w,
-                                const float* __restrict__ conv_b, const float* __restrict__ state, int64_t slot_stride,
+                                const float* __restrict__ conv_b, float* __restrict__ state, int64_t slot_stride,
                                 int64_t conv_off, const float* __restrict__ A_log, const float* __restrict__ dt_bias,
                                 const int* __restrict__ token_row, const int* __restrict__ row_start,
                                 const int* __restrict__ row_slot, float* __restrict__ act, float* __restrict__ dt,
-                                float* __restrict__ decay, int C, int H, int taps) {
+                                float* __restrict__ decay, int C, int H, int taps, int update_single) {
     pdl_wait();
     pdl_trigger();
     const int t = blockIdx.x;
     const int r = token_row[t];
     const int i0 = t - row_start[r];                    // index of the token within its row
-    const float* cstate = state + (int64_t)row_slot[r] * slot_stride + conv_off;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float* cstate = state + (int64_t)row_slot[r] * slot_stride + conv_off;
+    // A row of one token (a decoded token): its thread is the only one that reads the channel's memory in this
+    // step, so it also shifts the memory by the token's input (no kernel of its own for that in a decode step).
+    const bool shift = update_single && row_start[r + 1] - row_start[r] == 1;
+    // a block takes SSM_PREP_CHANNELS channels of a token (blockIdx.y): many short blocks hide the loads' latency
+    const int c_end = min(C, (int)(blockIdx.y + 1) * SSM_PREP_CHANNELS);
+    for (int c = blockIdx.y * SSM_PREP_CHANNELS + threadIdx.x; c < c_end; c += blockDim.x) {
         float acc = conv_b ? conv_b[c] : 0.f;
         for (int j = 0; j < taps; ++j) {
             const int idx = i0 - (taps - 1) + j;        // input index within the row; negative: before the step
@@ -56,7 +63,12 @@ __global__ void ssm_prep_kernel(const T* __restrict__ in, int64_t ld, int c0, in
             acc = fmaf(conv_w[(int64_t)c * taps + j], v, acc);
         }
         act[(int64_t)t * C + c] = acc * lr_sigmoid(acc);
+        if (shift) {
+            for (int j = 0; j + 1 < taps - 1; ++j) cstate[(int64_t)j * C + c] = cstate[(int64_t)(j + 1) * C + c];
+            if (taps > 1) cstate[(int64_t)(taps - 2) * C + c] = to_float(in[(int64_t)t * ld + c0 + c]);
+        }
     }
+    if (blockIdx.y != 0) return;
     for (int h = threadIdx.x; h < H; h += blockDim.x) {
         const float step = lr_softplus(to_float(in[(int64_t)t * ld + dt0 + h]) + dt_bias[h]);
         dt[(int64_t)t * H + h] = step;
@@ -65,16 +77,18 @@ __global__ void ssm_prep_kernel(const T* __restrict__ in, int64_t ld, int c0, in
 }
 
 extern "C" int acorn_ssm_prep(const void* in, int64_t ld, int c0, int dt0, const float* conv_w, const float* conv_b,
-                              const float* state, int64_t slot_stride, int64_t conv_off, const float* A_log,
+                              float* state, int64_t slot_stride, int64_t conv_off, const float* A_log,
                               const float* dt_bias, const int* token_row, const int* row_start, const int* row_slot,
                               float* act, float* dt, float* decay, int tokens, int C, int H, int taps, int dtype,
-                              cudaStream_t stream) {
+                              int update_single, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (taps < 1 || taps > SSM_MAX_TAPS || C < 1 || H < 0) return ACORN_ERR_UNSUPPORTED;
-    ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(ssm_prep_kernel<T>, dim3(tokens), dim3(256), 0, stream,
+    const int chunks = (C + SSM_PREP_CHANNELS - 1) / SSM_PREP_CHANNELS;
+    if (chunks > 65535) return ACORN_ERR_UNSUPPORTED;
+    ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(ssm_prep_kernel<T>, dim3(tokens, chunks), dim3(256), 0, stream,
                                                        (const T*)in, ld, c0, dt0, conv_w, conv_b, state, slot_stride,
                                                        conv_off, A_log, dt_bias, token_row, row_start, row_slot, act, dt,
-                                                       decay, C, H, taps));
+                                                       decay, C, H, taps, update_single));
     return ACORN_ERR_UNSUPPORTED;
 }
 
@@ -428,16 +442,45 @@ __global__ void gated_norm_kernel(const float* __restrict__ y, const T* __restri
     pdl_trigger();
     const int64_t t = blockIdx.x;
     const int part = W / groups, i0 = blockIdx.y * part;
+    // a part of at most GN_KEEP elements a thread stays in registers between the two passes
+    constexpr int GN_KEEP = 8;
+    const bool keep = part <= GN_KEEP * (int)blockDim.x;
+    float uu[GN_KEEP], zz[GN_KEEP];
     float ss = 0.f;
-    for (int i = threadIdx.x; i < part; i += blockDim.x) {
-        float u = y[t * W + i0 + i];
-        if (mode == 0) {
-            const float z = to_float(gate[t * ldg + i0 + i]);
-            u *= z * lr_sigmoid(z);
+    if (keep) {
+#pragma unroll
+        for (int k = 0; k < GN_KEEP; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            uu[k] = zz[k] = 0.f;
+            if (i < part) {
+                zz[k] = to_float(gate[t * ldg + i0 + i]);
+                uu[k] = y[t * W + i0 + i];
+                if (mode == 0) uu[k] *= zz[k] * lr_sigmoid(zz[k]);
+                ss += uu[k] * uu[k];
+            }
         }
-        ss += u * u;
+    } else {
+        for (int i = threadIdx.x; i < part; i += blockDim.x) {
+            float u = y[t * W + i0 + i];
+            if (mode == 0) {
+                const float z = to_float(gate[t * ldg + i0 + i]);
+                u *= z * lr_sigmoid(z);
+            }
+            ss += u * u;
+        }
     }
     const float inv = rsqrtf(block_sum(ss, scratch) / (float)part + eps);
+    if (keep) {
+#pragma unroll
+        for (int k = 0; k < GN_KEEP; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            if (i < part) {
+                const float u = mode == 0 ? uu[k] * inv * weight[i0 + i] : uu[k] * inv * weight[i0 + i] * lr_sigmoid(zz[k]);
+                out[t * ldo + i0 + i] = from_float<T>(u * out_scale);
+            }
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < part; i += blockDim.x) {
         const float z = to_float(gate[t * ldg + i0 + i]);
         float u = y[t * W + i0 + i];

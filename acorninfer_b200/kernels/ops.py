@@ -97,7 +97,8 @@ class _Sigs:
     acorn_add_into = [c_void_p, c_void_p, c_int64, c_int, c_void_p]
     acorn_head_gate = [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_float, c_int, c_void_p]
     acorn_ssm_prep = [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p,
-                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
+                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                      c_void_p]
     acorn_silu_rows = [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_void_p]
     acorn_linear_scan = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
                          c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
@@ -126,7 +127,7 @@ class _Sigs:
                         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
     acorn_conv_state_update = [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int, c_int,
-                               c_int, c_void_p]
+                               c_int, c_int, c_void_p]
     acorn_delta_rule = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                         c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
     acorn_delta_out = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p]
@@ -1195,11 +1196,12 @@ def delta_prep(main: torch.Tensor, up32: torch.Tensor, conv_w32: torch.Tensor, s
 
 
 def conv_state_update(main: torch.Tensor, state: torch.Tensor, conv_off: int, row_start: torch.Tensor,
-                      row_slot: torch.Tensor, num_rows: int, channels: int, taps: int) -> None:
-    """The last ``taps - 1`` convolution inputs of every row's request into its state."""
+                      row_slot: torch.Tensor, num_rows: int, channels: int, taps: int, skip_single: bool = False) -> None:
+    """The last ``taps - 1`` convolution inputs of every row's request into its state.  ``skip_single``: rows of
+    one token are left alone (the kernel before has shifted their memory: ``ssm_prep(update_single=True)``)."""
     _ok(lib().acorn_conv_state_update(main.data_ptr(), main.stride(0), state.data_ptr(), state.stride(0), int(conv_off),
                                       row_start.data_ptr(), row_slot.data_ptr(), num_rows, channels, taps,
-                                      dtype_code(main.dtype), _stream()), "conv_state_update")
+                                      dtype_code(main.dtype), 1 if skip_single else 0, _stream()), "conv_state_update")
 
 
 def delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, g: torch.Tensor,
@@ -1322,11 +1324,14 @@ def _rows2(t: torch.Tensor, name: str, dtype=None):
 
 def ssm_prep(proj: torch.Tensor, conv_col: int, dt_col: int, conv_w32: torch.Tensor, conv_b32: torch.Tensor | None,
              state: torch.Tensor, conv_off: int, a_log32: torch.Tensor, dt_bias32: torch.Tensor,
-             token_row: torch.Tensor, row_start: torch.Tensor, row_slot: torch.Tensor, taps: int):
+             token_row: torch.Tensor, row_start: torch.Tensor, row_slot: torch.Tensor, taps: int,
+             update_single: bool = False):
     """Of a projection ``proj`` [T, W]: the short causal convolution (``taps`` weights per channel, the last for
     the current token; inputs before the step from the request's state at ``conv_off``) with bias and silu of the
     ``C`` channels from column ``conv_col``, and of the ``H`` columns from ``dt_col`` the step sizes
-    ``softplus(. + dt_bias)`` and the decays ``exp(-exp(A_log) dt)``.  Returns float32 (act [T, C], dt [T, H], decay [T, H])."""
+    ``softplus(. + dt_bias)`` and the decays ``exp(-exp(A_log) dt)``.  Returns float32 (act [T, C], dt [T, H], decay [T, H]).
+    ``update_single``: the convolution's memory of rows of one token is shifted here as well (rows of more tokens
+    need ``conv_state_update(skip_single=True)`` after this)."""
     _rows2(proj, "proj")
     _check(state, "state", torch.float32, 2)
     _check(conv_w32, "conv weights", torch.float32, 2)
@@ -1342,7 +1347,7 @@ def ssm_prep(proj: torch.Tensor, conv_col: int, dt_col: int, conv_w32: torch.Ten
                              _ptr(conv_b32), state.data_ptr(), state.stride(0), int(conv_off), a_log32.data_ptr(),
                              dt_bias32.data_ptr(), token_row.data_ptr(), row_start.data_ptr(), row_slot.data_ptr(),
                              act.data_ptr(), dt.data_ptr(), decay.data_ptr(), T, C, H, taps, dtype_code(proj.dtype),
-                             _stream()), "ssm_prep")
+                             1 if update_single else 0, _stream()), "ssm_prep")
     return act, dt, decay
 
 

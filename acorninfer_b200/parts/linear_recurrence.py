@@ -87,9 +87,11 @@ class StateSpace(_RecurrentMixer):
         proj = ops.linear(x, self.w_in, out_dtype=self.ctx.dtype)             # [z | x | B | C | dt]
         conv_off = self.state_base + self.state_s
         act, dt, decay = ops.ssm_prep(proj, I, I + C, self.conv32, self.conv_b32, cache.state, conv_off, self.a_log32,
-                                      self.dt_bias32, inputs.token_row, inputs.row_start, inputs.row_slot, self.taps)
-        ops.conv_state_update(proj[:, I:I + C], cache.state, conv_off, inputs.row_start, inputs.row_slot,
-                              inputs.num_rows, C, self.taps)
+                                      self.dt_bias32, inputs.token_row, inputs.row_start, inputs.row_slot, self.taps,
+                                      update_single=True)
+        if inputs.plan.max_q_len > 1:       # rows of one token had their convolution memory shifted by ssm_prep
+            ops.conv_state_update(proj[:, I:I + C], cache.state, conv_off, inputs.row_start, inputs.row_slot,
+                                  inputs.num_rows, C, self.taps, skip_single=True)
         y = ops.linear_scan(act[:, I:I + GN], act[:, I + GN:], act[:, :I], decay, dt, self.d32, cache.state,
                             self.state_base, inputs.row_start, inputs.row_slot, inputs.num_rows, self.H, self.G,
                             self.N, self.V, longest_row=inputs.plan.max_q_len)
