@@ -48,6 +48,7 @@ struct AttnTcParams {
     const int* tiles;        // [n_tiles, 2]: row, first token of the tile within the row
     int table_stride, nq, nkv, logP, window;
     int chunk;               // > 0: a query sees the keys of its own block of `chunk` positions only
+    int keep;                // the request's first `keep` keys are seen whatever the window or block
     int n_tiles, pairs;      // pairs = ceil((nq / nkv) / 2): CTAs per (tile, kv head)
     float scale_log2;
 };
@@ -62,12 +63,12 @@ struct AttnTcParams {
 #define ATC_TMEM_COLS 512
 
 // -inf where the query at qpos may not see the key (causal, the first key its window or its block of positions
-// lets it see, rows beyond the tile's queries)
-__device__ __forceinline__ void atc_mask(float (&s)[64], int key0, int qpos, bool row_ok, int first_seen) {
+// lets it see, the request's first `keep` keys seen whatever the rule, rows beyond the tile's queries)
+__device__ __forceinline__ void atc_mask(float (&s)[64], int key0, int qpos, bool row_ok, int first_seen, int keep) {
 #pragma unroll
     for (int c = 0; c < 64; ++c) {
         const int key = key0 + c;
-        const bool okk = key <= qpos && row_ok && key >= first_seen;
+        const bool okk = key <= qpos && row_ok && (key >= first_seen || key < keep);
         s[c] = okk ? s[c] : -INFINITY;
     }
 }
@@ -154,7 +155,11 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
     int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
     if (p.chunk > 0) lo = max(lo, pos0 - pos0 % p.chunk);                // the first query's block of positions starts here
     lo &= ~(ATC_BN - 1);                                                 // blocks start at multiples of 128 keys
-    const int nb = (hi - lo + ATC_BN - 1) / ATC_BN;
+    // the kept first keys, where the rule's range starts beyond them, are nkb blocks of their own in front:
+    // block j holds keys from j * 128 (j < nkb) or from lo + (j - nkb) * 128
+    const int nkb = (p.keep > 0 && lo > 0) ? min((p.keep + ATC_BN - 1) / ATC_BN, lo / ATC_BN) : 0;
+    const int nb = nkb + (hi - lo + ATC_BN - 1) / ATC_BN;
+#define ATC_KEY0(j) ((j) < nkb ? (j) * ATC_BN : lo + ((j) - nkb) * ATC_BN)
 
     if (warp == 8) {
         // ---------------------------------------------------------------- producer
@@ -174,7 +179,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
         const int n_ops = ATC_BN / rows_per_op;                          // <= 16 (pages of 8 keys or more)
         const int first_key = p.page_base[r] << p.logP;
         auto row_of = [&](int j) -> int {
-            int key = lo + j * ATC_BN + (lane < n_ops ? lane : 0) * rows_per_op;
+            int key = ATC_KEY0(j) + (lane < n_ops ? lane : 0) * rows_per_op;
             // Rows no query of the tile may see (beyond the last query, or in pages a windowed
             // request has given back) are masked later: bring any rows that exist instead.
             if (key >= hi) key = hi - 1 - ((hi - 1) & (rows_per_op - 1));
@@ -286,9 +291,9 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
             good = __all_sync(0xffffffffu, good);
             if (!good) break;
             tc_fence_after();
-            const int key0 = lo + j * ATC_BN;
+            const int key0 = ATC_KEY0(j);
             // a block every query of the tile sees whole needs no mask
-            const bool masked = key0 + ATC_BN - 1 > pos0 || p.window > 0 || p.chunk > 0 || n_q < ATC_BM;
+            const bool masked = key0 + ATC_BN - 1 > pos0 || p.window > 0 || p.chunk > 0 || p.keep > 0 || n_q < ATC_BM;
             // One pass in the common case: exponentiate against the reference maximum the row
             // already has while the block's own maximum is taken; only a row whose maximum
             // outgrew the reference by more than 2^8 (always so in its first block) moves the
@@ -297,11 +302,11 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
             uint32_t w_lo[32], w_hi[32];
             float neg_ref = m_ref == -INFINITY ? 0.f : -m_ref;
             tmem_ld64(my_s, s);
-            if (masked) atc_mask(s, key0, qpos, row_ok, first_seen);
+            if (masked) atc_mask(s, key0, qpos, row_ok, first_seen, p.keep);
             float mx = atc_max(s);
             float psum = atc_exp_pack(s, p.scale_log2, neg_ref, w_lo);
             tmem_ld64(my_s + 64, s);
-            if (masked) atc_mask(s, key0 + 64, qpos, row_ok, first_seen);
+            if (masked) atc_mask(s, key0 + 64, qpos, row_ok, first_seen, p.keep);
             mx = fmaxf(mx, atc_max(s)) * p.scale_log2;                   // the scale is positive
             float corr = 1.f;
             const bool grew = mx > m_ref + ATC_RESCALE_LOG2;
@@ -314,7 +319,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
                 }
                 psum = atc_exp_pack(s, p.scale_log2, neg_ref, w_hi);
                 tmem_ld64(my_s, s);
-                if (masked) atc_mask(s, key0, qpos, row_ok, first_seen);
+                if (masked) atc_mask(s, key0, qpos, row_ok, first_seen, p.keep);
                 psum += atc_exp_pack(s, p.scale_log2, neg_ref, w_lo);
             } else {
                 psum += atc_exp_pack(s, p.scale_log2, neg_ref, w_hi);
@@ -383,14 +388,14 @@ extern "C" int acorn_attention_prefill_tc(const void* q, int64_t q_stride, int t
                                           const void* v_pages, int64_t num_pages, const int* block_table,
                                           const int* page_base, int table_stride, const int* row_start,
                                           const int* row_pos, const int* tiles, int n_tiles, int nq, int nkv, int d,
-                                          int P, float scale, int window, int chunk, cudaStream_t stream) {
+                                          int P, float scale, int window, int chunk, int keep, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (!acorn_attention_prefill_tc_supported(nq, nkv, d, P) || q_stride % 8 != 0 || ((uintptr_t)q & 15))
         return ACORN_ERR_UNSUPPORTED;
     AttnTcParams p;
     p.out = (bf16*)out; p.block_table = block_table; p.page_base = page_base; p.row_start = row_start;
     p.row_pos = row_pos; p.tiles = tiles; p.table_stride = table_stride; p.nq = nq; p.nkv = nkv;
-    p.logP = acorn_log2_exact_tc(P); p.window = window; p.chunk = chunk; p.scale_log2 = scale * 1.4426950408889634f;
+    p.logP = acorn_log2_exact_tc(P); p.window = window; p.chunk = chunk; p.keep = keep; p.scale_log2 = scale * 1.4426950408889634f;
     p.n_tiles = n_tiles; p.pairs = (nq / nkv + 1) / 2;
     const int64_t ctas = (int64_t)n_tiles * nkv * p.pairs;
     if (ctas > 0x7fffffff) return ACORN_ERR_UNSUPPORTED;

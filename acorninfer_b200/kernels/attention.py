@@ -124,8 +124,8 @@ def paged_attention(qkv: torch.Tensor, inputs, group, cache, nq: int, nkv: int, 
                     value_dim: int | None = None) -> torch.Tensor:
     """Attention of all tokens of the step; q is the head of ``qkv`` ([T, >= nq d]).  ``window``, ``chunk``,
     ``keep_first``: which earlier keys a query reads (see ``parts/attention.py``); ``value_dim``: width of the
-    value rows where it is not ``d``.  The tensor-core kernels take values as wide as keys; the tcgen05 prefill
-    kernel knows windows and blocks of positions, the TMA decode kernel windows only."""
+    value rows where it is not ``d``.  The tensor-core kernels take values as wide as keys; the TMA decode kernel
+    knows windows only."""
     P = cache.k_pages.shape[2]
     windowed_only = not chunk and not keep_first
     mask = {"chunk": chunk, "keep_first": keep_first}
@@ -144,12 +144,12 @@ def paged_attention(qkv: torch.Tensor, inputs, group, cache, nq: int, nkv: int, 
             # a mixed step: prompt portions through the prefill kernel, decoded tokens through the
             # decode kernel, both writing their rows of one output
             out = torch.empty((inputs.num_tokens, nq * d), dtype=qkv.dtype, device=qkv.device)
-            if not keep_first and ops.attention_prefill_tc_supported(nq, nkv, d, P) and qkv.stride(0) % 8 == 0:
+            if ops.attention_prefill_tc_supported(nq, nkv, d, P) and qkv.stride(0) % 8 == 0:
                 # long rows on the tcgen05 kernel (tiles of 128 queries), short ones on the mma.sync kernel
                 if hx["attention.q_tiles_large"].shape[0]:
                     ops.attention_prefill_tc(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,
                                              group.page_base, inputs.row_start, inputs.row_pos, x["attention.q_tiles_large"],
-                                             inputs.num_tokens, nq, nkv, d, scale, window, out=out, chunk=chunk)
+                                             inputs.num_tokens, nq, nkv, d, scale, window, out=out, **mask)
                 if hx["attention.q_tiles_small"].shape[0]:
                     ops.attention_prefill(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,
                                           group.page_base, inputs.row_start, inputs.row_pos, x["attention.q_tiles_small"],

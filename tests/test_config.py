@@ -93,8 +93,10 @@ def test_presets_of_the_family_are_valid_configurations():
         cfg = config_from_dict(raw)
         if name.startswith("qwen3"):
             assert cfg.head_dim == 128 and cfg.num_attention_heads % cfg.num_key_value_heads == 0
+        elif name.startswith("kogonex"):
+            assert len(cfg.layers) == 10 and cfg.layers[4].mixer.kv_from == 1
         else:
-            assert name.startswith("kogonex") and len(cfg.layers) == 10 and cfg.layers[4].mixer.kv_from == 1
+            assert name.startswith("vagulorn") and [l.type for l in cfg.layers[:4]] == ["mamba2", "attention", "parallel", "mamba2"]
         spec_for(cfg)                                    # builds the model description
     assert preset("Qwen3-8B")["hidden_size"] == 4096
     import pytest

@@ -289,9 +289,8 @@ def _attention_case(befores, qlens, P, d, dv, nq, nkv, rule, size, keep, spikes,
         big = 32 if kernel.startswith("tc") else 10 ** 9          # rows from 32 tokens on go to the tcgen05 kernel
         tiles = torch.tensor([(r, q0) for r, n in enumerate(qlens) if n >= big for q0 in range(0, n, 128)], **i32).view(-1, 2)
         if tiles.shape[0]:
-            assert keep == 0
             o.attention_prefill_tc(q_new, nq * d, *common, torch.tensor(starts, **i32), torch.tensor(befores, **i32), tiles,
-                                   lay["num_tokens"], nq, nkv, d, scale, window, out=out, chunk=chunk)
+                                   lay["num_tokens"], nq, nkv, d, scale, window, out=out, chunk=chunk, keep_first=keep)
         tiles = torch.tensor([(r, q0) for r, n in enumerate(qlens) if 1 < n < big for q0 in range(0, n, 64)], **i32).view(-1, 2)
         if tiles.shape[0]:
             o.attention_prefill(q_new, nq * d, *common, torch.tensor(starts, **i32), torch.tensor(befores, **i32), tiles,
@@ -313,7 +312,7 @@ KERNELS = [(torch.float32, 2e-5, "plain", 24, 40, 6, 3), (torch.bfloat16, 2e-2, 
            (torch.bfloat16, 2e-2, "mma2", 128, 128, 8, 1)]
 
 
-@pytest.mark.parametrize("dtype,tol,kernel,d,dv,nq,nkv", KERNELS)
+@pytest.mark.parametrize("dtype,tol,kernel,d,dv,nq,nkv", KERNELS + [(torch.bfloat16, 2e-2, "tc2", 128, 128, 8, 2)])
 def test_attention_window_with_kept_first_keys(dtype, tol, kernel, d, dv, nq, nkv):
     """A key that outweighs all others is seen up to the query window - 1 tokens after it and no longer, in a
     prompt's rows and in single decoded tokens, at page borders; the first ``keep`` keys are seen from
@@ -335,6 +334,10 @@ def test_attention_window_with_kept_first_keys(dtype, tol, kernel, d, dv, nq, nk
         got, want = _attention_case([0, 99, 40], [70, 1, 3], P, d, dv, nq, nkv, "window", W2, keep2, [(0, 20), (1, 20), (2, 20)],
                                     dtype, kernel, seed=W2)
         assert (got - want).abs().max() < tol, (W2, keep2)
+    # kept keys that fill more than one block of 128 keys, far in front of the window
+    got, want = _attention_case([0, 400], [700, 200], P, d, dv, nq, nkv, "window", 40, 150, [(0, 149), (0, 150), (1, 10), (1, 140)],
+                                dtype, kernel, seed=9)
+    assert (got - want).abs().max() < tol
 
 
 @pytest.mark.parametrize("dtype,tol,kernel,d,dv,nq,nkv", KERNELS + [(torch.bfloat16, 2e-2, "tc2", 128, 128, 8, 2)])
