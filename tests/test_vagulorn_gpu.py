@@ -21,7 +21,7 @@ from tests import traces
 from tests.paged import rows_layout, scatter_to_pages
 from tests.plain import vagulorn as plain
 from tests.tiny import random_tokens
-from tests.vagulorn_tiny import VAGU_LONG, VAGUS, L, att, beside, make_model_dir, read_weights
+from tests.vagulorn_tiny import VAGU_LONG, VAGUS, L, att, beside, make_model_dir, random_config, read_weights
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -169,6 +169,26 @@ def test_long_requests_blocks_and_windows_over_pages(tmp_path):
             got, runner = run_cut(tiny, d, build(reqs), dtype)
             assert len(got) == sum(len(t) for t in reqs.values())
             check(got, ref, dtype, f"long, {cut}")
+
+
+@pytest.mark.parametrize("seed", [1, 4, 9, 13, 16])
+def test_configurations_drawn_at_random(seed, tmp_path):
+    """Models whose sizes are drawn from what real models have (heads of 32 to 128, also with the whole head
+    rotated; states up to 128; values wider than keys; windows of 32 to 256), requests of up to 600 tokens, whole
+    and mixed in a small pool, float32 and bfloat16."""
+    import random
+    tiny = dict(cfg=random_config(seed), page_size=16, seed=seed)
+    d = make_model_dir(tmp_path, tiny, sigma=0.06, sigma_norm=0.1)
+    w = read_weights(d)
+    rng = random.Random(seed)
+    lengths = [rng.randint(300, 600), rng.randint(100, 300), rng.randint(2, 60), 1, rng.randint(60, 200)]
+    reqs = {f"q{i}": random_tokens(n, tiny["cfg"].vocab_size, seed * 10 + i) for i, n in enumerate(lengths)}
+    ref = {rid: plain.forward(tiny["cfg"].to_dict(), w, toks).numpy() for rid, toks in reqs.items()}
+    for dtype, tol in (("float32", 6e-5), ("bfloat16", 0.15)):
+        for cut, steps in (("whole", traces.whole(reqs)), ("decode_tail", traces.decode_tail(reqs, tail=40)),
+                           ("mixed", traces.mixed(reqs, max_live=4, seed=seed, max_portion=90, stagger=1))):
+            got, _ = run_cut(tiny, d, steps, dtype)
+            check(got, ref, dtype, f"seed {seed}, {cut}", tol=tol)
 
 
 def follows_plain(cfg, w, prompt, ids, slack):

@@ -82,3 +82,43 @@ def read_weights(model_dir: Path) -> dict[str, torch.Tensor]:
 
 def make_model_dir(tmp: Path, tiny: dict, sigma: float = 0.12, sigma_norm: float = 0.2) -> Path:
     return write_random_model(tmp, tiny["cfg"], tiny["seed"], sigma, sigma_norm)
+
+
+def random_config(seed: int) -> VagulornConfig:
+    """A configuration drawn at random: 3 to 5 layers with each kind of mixer at least once, widths, head counts,
+    key, value and state sizes, rotated parts, blocks, windows, kept keys, taps and norm parts from lists that hold
+    the sizes real models have (heads of 32 to 128, states of 16 to 128) beside odd ones."""
+    import random
+    rng = random.Random(seed)
+    width = rng.choice([128, 192, 320, 384])
+    kinds = ["attention", "parallel", "mamba2"]
+    n = rng.randint(3, 5)
+    order = [rng.choice(kinds) for _ in range(n)]
+    for k in kinds:
+        if k not in order:
+            order[rng.randrange(n)] = k
+    layers = []
+    for k in order:
+        ff = rng.choice([None, 200, 256, 384])
+        if k == "attention":
+            d, kv = rng.choice([32, 64, 96, 128]), rng.choice([1, 2, 4])
+            dv, rd = rng.choice([d, d, 64, 160]), rng.choice([d, d // 2, d // 4])
+            if rng.random() < 0.4:
+                d = dv = rd = 128                       # whole head rotated: the products' own rotary epilogue where it applies
+            layers.append(L(att(kv * rng.choice([1, 2, 3, 4]), kv, d, dv, d ** -0.5, rot_dims=rd, rot_base=rng.choice([1e4, 3e5]),
+                                mask_size=rng.choice([32, 64, 100, 256])), ff))
+        elif k == "parallel":
+            d, kv = rng.choice([32, 64, 96, 128]), rng.choice([1, 2])
+            hr = rng.choice([1, 2, 4, 8])
+            layers.append(L(beside(att(kv * rng.choice([1, 2, 4]), kv, d, d, d ** -0.5, rot_dims=rng.choice([d, d // 2]),
+                                       mask_size=rng.choice([32, 64, 100]), keep_first=rng.choice([0, 1, 4, 20])),
+                                   heads=hr, dim=rng.choice([16, 32, 64, 128]), vdim=rng.choice([16, 32, 64, 128]),
+                                   decay=[rng.choice([0.5, 0.9, 0.99, 0.999]) for _ in range(hr)],
+                                   left_scale=rng.choice([0.5, 1.0]), right_scale=rng.choice([0.7, 1.2])), ff))
+        else:
+            g = rng.choice([1, 2, 4])
+            heads = g * rng.choice([1, 2, 4])
+            layers.append(L(StateSpaceConfig(heads=heads, vdim=rng.choice([16, 32, 48, 64]), state=rng.choice([16, 48, 64, 128]),
+                                             groups=g, conv=rng.choice([2, 3, 4]), norm_groups=rng.choice([1, 2, heads])), ff))
+    return VagulornConfig(vocab_size=rng.choice([300, 512, 1000]), hidden_size=width, norm_eps=rng.choice([1e-5, 1e-6]),
+                          embedding_scale=rng.choice([1.0, 8.0, 20.0]), layers=tuple(layers))
